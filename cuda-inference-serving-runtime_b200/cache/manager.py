@@ -5,8 +5,11 @@ Run entries of the model are sorted into groups by what their mixer needs
 (`CacheUse.group_key()`): all entries that keep every key with the same geometry share
 one page pool and one block table per request; entries that keep a window of keys form
 another group with pages of their own, and give a page back as soon as the window has
-passed it; entries with fixed-size state get a tensor [slots, ...] each.  A page id
-means the same page in every entry of its group, so one allocation serves all of them.
+passed it (pages that hold the first `keep_first` keys of such a use stay); entries with
+fixed-size state get a tensor [slots, ...] each.  A page id means the same page in every
+entry of its group, so one allocation serves all of them.  A paged entry may hold a small
+state besides its pages (`side_states`: the kept inputs of a convolution, say): always its
+own, also where it reads another entry's pages.
 
 Every live request holds one slot.  The slot indexes the request's row in each
 group's block table on the device and its row in every state tensor.  Block tables
@@ -39,6 +42,8 @@ class PagedBinding:
     page_size: int
     write: bool                  # False: the entry reads another entry's pages
     window: Optional[int]
+    keep_first: int = 0          # the sequence's first keys that stay (and stay in sight) behind the window
+    state: Optional[torch.Tensor] = None     # the entry's own side state [slots, ...], where its mixer asked for one
 
 
 @dataclass
@@ -96,11 +101,13 @@ class CacheManager:
 
     `uses[i]` is the `CacheUse` of run entry i, or the index of the earlier entry whose
     cache entry i reads.  `n_pages` pages of `page_size` tokens are given to each page
-    group.  With `device=None` only the host bookkeeping exists (tests of the allocator).
+    group.  `side_states[i]`, where given, is a `CacheUse("state", ...)` that run entry i holds besides
+    its pages (or besides the pages it reads).  With `device=None` only the host bookkeeping exists
+    (tests of the allocator).
     """
 
     def __init__(self, uses: Sequence, n_pages: int, page_size: int, max_slots: int, max_positions: int,
-                 dtype: torch.dtype = torch.float32, device=None):
+                 dtype: torch.dtype = torch.float32, device=None, side_states: Optional[Sequence] = None):
         if n_pages <= 0 or page_size <= 0 or max_slots <= 0:
             raise ValueError("cache dimensions must be positive")
         self.page_size, self.max_slots, self.max_positions = page_size, max_slots, max_positions
@@ -132,6 +139,18 @@ class CacheManager:
                     self.entry_group[e] = ("state", group.index)
             else:
                 raise ValueError(f"unknown cache use {use.kind!r}")
+        self.entry_side: Dict[int, Tuple[int, int]] = {}    # run entry -> (state group index, index inside it) of its side state
+        by_side: Dict[tuple, List[int]] = {}
+        for entry, use in enumerate(side_states or ()):
+            if use is not None:
+                if use.kind != "state":
+                    raise ValueError("a side state is a fixed-size tensor per request (kind \"state\")")
+                by_side.setdefault(use.group_key(), []).append(entry)
+        for entries in by_side.values():
+            group = StateGroup(len(self.state_groups), side_states[entries[0]], entries, max_slots, device)
+            self.state_groups.append(group)
+            for e in entries:
+                self.entry_side[e] = (group.index, group.entry_slot[e])
         self.requests: Dict[object, _Request] = {}
         self.free_slots: List[int] = list(reversed(range(max_slots)))
 
@@ -246,7 +265,8 @@ class CacheManager:
             # the next query sits at position `length` and sees keys > length - window
             dead = max(0, (req.length - g.use.window + 1) // g.page_size)
             table = req.tables[g.index]
-            for logical in range(req.first_live[g.index], min(dead, len(table))):
+            kept = -(-g.use.keep_first // g.page_size)       # pages that hold kept first keys never go back
+            for logical in range(max(req.first_live[g.index], kept), min(dead, len(table))):
                 if table[logical] >= 0:
                     g.pool.release(table[logical])
                     table[logical] = -1
@@ -293,8 +313,10 @@ class CacheManager:
         if kind == "pages":
             g = self.page_groups[gi]
             e = g.entry_slot[source]
+            side = self.entry_side.get(entry)
+            state = None if side is None else self.state_groups[side[0]].storage[side[1]]
             return PagedBinding(g.storage[e, 0], g.storage[e, g.use.planes - 1], g.device_table, g.page_size,
-                                write=reads_from is None, window=g.use.window)
+                                write=reads_from is None, window=g.use.window, keep_first=g.use.keep_first, state=state)
         g = self.state_groups[gi]
         return StateBinding(g.storage[g.entry_slot[source]])
 
@@ -311,7 +333,8 @@ class CacheManager:
                 if list(row[: len(table)]) != table or (row[len(table):] != -1).any():
                     raise AssertionError(f"block table row of {key!r} disagrees with its page list")
                 for logical, page in enumerate(table):
-                    live = g.use.window is None or (logical + 1) * g.page_size > req.length - g.use.window + 1
+                    live = (g.use.window is None or (logical + 1) * g.page_size > req.length - g.use.window + 1
+                            or logical * g.page_size < g.use.keep_first)
                     if live and logical * g.page_size < req.length and page < 0:
                         raise AssertionError(f"sequence {key!r} lost page {logical} that it still needs")
         slots = [req.slot for req in self.requests.values()]

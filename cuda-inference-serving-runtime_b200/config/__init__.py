@@ -5,8 +5,9 @@ from .registry import ARCHITECTURES, Architecture, architecture_for, register_ar
 from .llama import LlamaConfig      # registers LlamaForCausalLM
 from .zurolorn import ZurolornConfig    # registers Zurolorn
 from .ronolorn import RonolornConfig    # registers Ronolorn
+from .gipozen import GipozenConfig      # registers Gipozen
 from .presets import preset, preset_dict, preset_names
 
-__all__ = ["CacheUse", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "LlamaConfig", "ZurolornConfig", "RonolornConfig",
+__all__ = ["CacheUse", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "LlamaConfig", "ZurolornConfig", "RonolornConfig", "GipozenConfig",
            "ARCHITECTURES", "Architecture", "architecture_for", "register_architecture",
            "preset", "preset_dict", "preset_names"]

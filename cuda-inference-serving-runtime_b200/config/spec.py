@@ -61,8 +61,9 @@ class CacheUse:
     """What a mixer needs from the cache manager.
 
     kind "pages": keys and values in pages ([kv_heads, page, head_dim] per page);
-    `window` None keeps every key, an integer keeps the last `window` of them.  `planes` 2: a key plane and a value
-    plane; 1: one plane of rows that serve as both (a latent from which keys and values are derived).
+    `window` None keeps every key, an integer keeps the last `window` of them, and with it `keep_first` also the
+    sequence's first `keep_first` keys (their pages are never given back while the request lives).  `planes` 2: a key
+    plane and a value plane; 1: one plane of rows that serve as both (a latent from which keys and values are derived).
     kind "state": a fixed-size tensor per request of `state_shape`/`state_dtype`.
     kind "none": nothing.
     """
@@ -73,9 +74,11 @@ class CacheUse:
     state_shape: Tuple[int, ...] = ()
     state_dtype: str = "float32"
     planes: int = 2
+    keep_first: int = 0
 
     def group_key(self) -> tuple:
-        return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shape, self.state_dtype, self.planes)
+        return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shape, self.state_dtype, self.planes,
+                self.keep_first if self.window is not None else 0)
 
 
 @dataclass(frozen=True)

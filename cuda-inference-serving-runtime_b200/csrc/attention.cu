@@ -17,6 +17,9 @@
 // kernels/ops.cu:35-86 (split + merge), runtime/reference.py:18-31 (grouping
 // h -> h / (Hq/Hkv), scale, causal order) of nehanmohammed19/cuda-inference-serving-runtime.
 // Cache layout: [pages, kv_heads, page_size, HEAD_DIM].
+//
+// Visibility: query i sees key j when j <= i and (window <= 0 or i - j < window or j < keep_first): a window of the
+// latest keys, and optionally the sequence's first `keep_first` keys kept in sight whatever the distance.
 #include "common.cuh"
 
 #ifndef HEAD_DIM
@@ -66,7 +69,7 @@ attn_prefill_kernel(const st_t* __restrict__ q, st_t* __restrict__ out, const st
                     const st_t* __restrict__ v_cache, const int* __restrict__ req_slot,
                     const int* __restrict__ block_table, int table_width, const int* __restrict__ tile_req, const int* __restrict__ tile_q0,
                     const int* __restrict__ q_start, const int* __restrict__ q_len,
-                    const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window, float sink) {
+                    const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window, int keep_first, float sink) {
     CISR_TRACE_SCOPE(TRACE_ATTN_SIMT);
     extern __shared__ __align__(16) float smem[];
     float* Qs = smem;             // [D][QS]   transposed, pre-scaled
@@ -107,7 +110,12 @@ attn_prefill_kernel(const st_t* __restrict__ q, st_t* __restrict__ out, const st
     const int k_end = qpos0 + rows;  // one past the last key any row of the tile sees
     int k_first = 0;
     if (window > 0) k_first = max(0, qpos0 - window + 1);
-    for (int k0 = (k_first / BN) * BN; k0 < k_end; k0 += BN) {
+    // key tiles: those that hold kept first keys, then from the window's first tile on (the two runs never overlap)
+    const int k_begin = (k_first / BN) * BN;
+    const int n_kept = (window > 0 && keep_first > 0) ? min((keep_first + BN - 1) / BN, k_begin / BN) : 0;
+    const int n_key_tiles = n_kept + (k_end - k_begin + BN - 1) / BN;
+    for (int kt = 0; kt < n_key_tiles; ++kt) {
+        const int k0 = kt < n_kept ? kt * BN : k_begin + (kt - n_kept) * BN;
         __syncthreads();  // previous tile's readers are done (also orders the Q stores on the first pass)
         for (int e = tid; e < BN * NVEC; e += PREFILL_THREADS) {
             const int r = e / NVEC, c = (e - r * NVEC) * VEC;
@@ -159,7 +167,7 @@ attn_prefill_kernel(const st_t* __restrict__ q, st_t* __restrict__ out, const st
 #pragma unroll
             for (int j = 0; j < NJ; ++j) {
                 const int kpos = k0 + tx * NJ + j;
-                const bool ok = (r < rows) && (kpos <= qpos) && (window <= 0 || kpos + window > qpos);
+                const bool ok = (r < rows) && (kpos <= qpos) && (window <= 0 || kpos + window > qpos || kpos < keep_first);
                 s[i][j] = ok ? s[i][j] : -INFINITY;
                 tile_max = fmaxf(tile_max, s[i][j]);
             }
@@ -226,7 +234,7 @@ __global__ void __launch_bounds__(DEC_THREADS)
 attn_decode_kernel(const st_t* __restrict__ q, const st_t* __restrict__ k_cache, const st_t* __restrict__ v_cache,
                    const int* __restrict__ req_slot, const int* __restrict__ block_table, int table_width, const int* __restrict__ dec_req,
                    const int* __restrict__ q_start, const int* __restrict__ ctx_len, float* __restrict__ partial,
-                   float* __restrict__ stats, int hq, int hkv, int page_size, float scale, int window,
+                   float* __restrict__ stats, int hq, int hkv, int page_size, float scale, int window, int keep_first,
                    int split_size, int n_splits) {
     CISR_TRACE_SCOPE(TRACE_ATTN_SIMT);
     extern __shared__ __align__(16) float smem[];
@@ -247,8 +255,8 @@ attn_decode_kernel(const st_t* __restrict__ q, const st_t* __restrict__ k_cache,
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int* table = block_table + (size_t)req_slot[req] * table_width;
 
-    int lo = split * split_size, hi = min(lo + split_size, ctx);
-    if (window > 0) lo = max(lo, ctx - window);
+    const KeyRun run = decode_key_run(split, split_size, ctx, window, keep_first);
+    const int lo = run.lo, hi = run.hi;
 
     const size_t part_base = ((size_t)slot * hq + (size_t)kvh * group) * n_splits;  // + g * n_splits + split
     if (lo >= hi) {  // nothing in this range: the merge skips entries with denominator 0
@@ -300,7 +308,8 @@ attn_decode_kernel(const st_t* __restrict__ q, const st_t* __restrict__ k_cache,
                 acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc);
                 acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
             }
-            ps[g * TK + t] = (k0 + t < hi) ? acc : -INFINITY;
+            const int kpos = k0 + t;
+            ps[g * TK + t] = (kpos < hi && !in_gap(run, kpos)) ? acc : -INFINITY;
         }
         __syncthreads();
 
@@ -309,7 +318,7 @@ attn_decode_kernel(const st_t* __restrict__ q, const st_t* __restrict__ k_cache,
             for (int t = lane; t < TK; t += 32) mx = fmaxf(mx, ps[g * TK + t]);
             mx = warp_max(mx);
             const float m_old = m_s[g];
-            const float m_new = fmaxf(m_old, mx);  // finite: the range holds at least one key
+            const float m_new = fmaxf(m_old, mx);  // finite: the run's first tile holds a key in sight
             float sum = 0.f;
             for (int t = lane; t < TK; t += 32) {
                 const float pr = expf(ps[g * TK + t] - m_new);
@@ -386,7 +395,7 @@ CISR_EXPORT int cisr_attn_prefill_tile() { return BM; }
 CISR_EXPORT int cisr_attn_prefill(const void* q, void* out, const void* k_cache, const void* v_cache,
                                   const int* req_slot, const int* block_table, int table_width, const int* tile_req, const int* tile_q0,
                                   int n_tiles, const int* q_start, const int* q_len, const int* ctx_len, int hq,
-                                  int hkv, int page_size, float scale, int window, float sink, void* stream) {
+                                  int hkv, int page_size, float scale, int window, int keep_first, float sink, void* stream) {
     if (n_tiles <= 0) return 0;
     if (hq % hkv) return -2;
     static bool configured = false;
@@ -397,7 +406,7 @@ CISR_EXPORT int cisr_attn_prefill(const void* q, void* out, const void* k_cache,
     }
     attn_prefill_kernel<<<dim3(n_tiles, hq), PREFILL_THREADS, PREFILL_SMEM, (cudaStream_t)stream>>>(
         (const st_t*)q, (st_t*)out, (const st_t*)k_cache, (const st_t*)v_cache, req_slot, block_table, table_width, tile_req,
-        tile_q0, q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, sink);
+        tile_q0, q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, keep_first, sink);
     return launch_status();
 }
 
@@ -405,7 +414,7 @@ CISR_EXPORT int cisr_attn_prefill(const void* q, void* out, const void* k_cache,
 CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
                                  const int* req_slot, const int* block_table, int table_width, const int* dec_req, int n_dec,
                                  const int* q_start, const int* ctx_len, float* partial, float* stats, int hq,
-                                 int hkv, int page_size, float scale, int window, int split_size, int n_splits,
+                                 int hkv, int page_size, float scale, int window, int keep_first, int split_size, int n_splits,
                                  float sink, void* stream) {
     if (n_dec <= 0) return 0;
     if (hq % hkv || split_size <= 0 || n_splits <= 0) return -2;
@@ -420,7 +429,7 @@ CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, 
     cudaStream_t s = (cudaStream_t)stream;
     attn_decode_kernel<<<dim3(n_dec, hkv, n_splits), DEC_THREADS, smem, s>>>(
         (const st_t*)q, (const st_t*)k_cache, (const st_t*)v_cache, req_slot, block_table, table_width, dec_req, q_start,
-        ctx_len, partial, stats, hq, hkv, page_size, scale, window, split_size, n_splits);
+        ctx_len, partial, stats, hq, hkv, page_size, scale, window, keep_first, split_size, n_splits);
     int status = launch_status();
     if (status) return status;
     attn_merge_kernel<<<dim3(n_dec, hq), D < 128 ? 64 : 128, 0, s>>>(partial, stats, (st_t*)out, dec_req, q_start, hq, n_splits, sink);

@@ -120,7 +120,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
                         const bf16* __restrict__ v_cache, const int* __restrict__ req_slot,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ tile_req,
                         const int* __restrict__ tile_q0, const int* __restrict__ q_start, const int* __restrict__ q_len,
-                        const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window, float sink) {
+                        const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window, int keep_first, float sink) {
     CISR_TRACE_SCOPE(TRACE_ATTN_PREFILL);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][LDS]
@@ -158,8 +158,16 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
     int k_first = 0;
     if (window > 0) k_first = max(0, qpos0 - window + 1);
     const int k_begin = (k_first / BN) * BN;
-    const int n_tiles = (k_end - k_begin + BN - 1) / BN;
+    // key tiles: those that hold kept first keys (their page entries are read from the table itself), then from the
+    // window's first tile on; the two runs never overlap
+    const int n_kept = (window > 0 && keep_first > 0) ? min((keep_first + BN - 1) / BN, k_begin / BN) : 0;
+    const int n_tiles = n_kept + (k_end - k_begin + BN - 1) / BN;
     const int first_page = k_begin / page_size;
+    auto tile_k0 = [&](int t) { return t < n_kept ? t * BN : k_begin + (t - n_kept) * BN; };
+    auto load_tile = [&](bf16* Kt, int t) {
+        if (t < n_kept) load_kv_tile<128>(Kt, Kt + BN * LDS, k_cache, v_cache, table, 0, t * BN, k_end, hkv, kvh, page_size, gtid);
+        else load_kv_tile<128>(Kt, Kt + BN * LDS, k_cache, v_cache, pages, first_page, tile_k0(t), k_end, hkv, kvh, page_size, gtid);
+    };
     cp_async_wait<0>();
     __syncthreads();                              // Q and the page entries are in shared memory
 
@@ -174,20 +182,16 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
     const float scale2 = scale * LOG2E;
 
     bf16* gbuf = pipe + (size_t)group * NB * 2 * BN * LDS;      // this group's [K tile | V tile] buffers
-    if (group < n_tiles)
-        load_kv_tile<128>(gbuf, gbuf + BN * LDS, k_cache, v_cache, pages, first_page, k_begin + group * BN, k_end, hkv, kvh,
-                          page_size, gtid);
+    if (group < n_tiles) load_tile(gbuf, group);
     cp_async_commit();
 
     for (int t = group, it = 0; t < n_tiles; t += NG, ++it) {
-        const int k0 = k_begin + t * BN;
+        const int k0 = tile_k0(t);
         const int buf = NB == 2 ? (it & 1) : 0;
         cp_async_wait<0>();
         group_sync(group);                    // tile t has landed; the group is done with the other buffer
         if (NB == 2 && t + NG < n_tiles) {
-            bf16* nb = gbuf + (buf ^ 1) * 2 * BN * LDS;
-            load_kv_tile<128>(nb, nb + BN * LDS, k_cache, v_cache, pages, first_page, k0 + NG * BN, k_end, hkv, kvh, page_size,
-                              gtid);          // keys from k_end on are masked for every row
+            load_tile(gbuf + (buf ^ 1) * 2 * BN * LDS, t + NG);       // keys from k_end on are masked for every row
         }
         cp_async_commit();
         const bf16* Kt = gbuf + buf * 2 * BN * LDS;
@@ -211,7 +215,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
         // tiles of a long prompt lie wholly inside and skip the per-element test.
         const int warp_row0 = warp * 16;
         const bool inside = (k0 + BN - 1 <= qpos0 + warp_row0) && (warp_row0 + 15 < rows) &&
-                            (window <= 0 || k0 + window > qpos0 + warp_row0 + 15);
+                            (window <= 0 || k0 + window > qpos0 + warp_row0 + 15 || k0 + BN <= keep_first);
         float tile_max[2] = {-INFINITY, -INFINITY};
         if (inside) {
 #pragma unroll
@@ -227,7 +231,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
                     const int row = warp_row0 + (lane >> 2) + 8 * (e >> 1);
                     const int kpos = k0 + nt * 8 + 2 * (lane & 3) + (e & 1);
                     const int qpos = qpos0 + row;
-                    const bool ok = (row < rows) && (kpos <= qpos) && (window <= 0 || kpos + window > qpos);
+                    const bool ok = (row < rows) && (kpos <= qpos) && (window <= 0 || kpos + window > qpos || kpos < keep_first);
                     const float v = ok ? s[nt][e] : -INFINITY;
                     s[nt][e] = v;
                     tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
@@ -273,7 +277,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
         }
         if (NB == 1 && t + NG < n_tiles) {
             group_sync(group);                // every warp of the group is done with the only buffer
-            load_kv_tile<128>(gbuf, gbuf + BN * LDS, k_cache, v_cache, pages, first_page, k0 + NG * BN, k_end, hkv, kvh, page_size, gtid);
+            load_tile(gbuf, t + NG);
             cp_async_commit();
         }
     }
@@ -351,10 +355,10 @@ struct PaddedTile {
     __device__ __forceinline__ const void* v_at(int row, int chunk) const { return v + row * LDS + chunk * 8; }
 };
 // A warp's share of one 64-key tile: its 16-key slab against the group's query rows, with the running softmax.
-// k0 is the position of the slab's first key; keys outside [lo, hi) are masked.
+// k0 is the position of the slab's first key; keys outside the run [lo, hi) and keys of its gap are masked.
 template <typename Tile>
 __device__ __forceinline__ void decode_slab(const Tile& tile, const uint32_t (&qf)[KD][4], float (&o)[ND][4], float (&m_run)[2],
-                                            float (&l_run)[2], int k0, int lo, int hi, float scale2, int warp, int lane) {
+                                            float (&l_run)[2], int k0, const KeyRun& run, float scale2, int warp, int lane) {
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
     for (int kk = 0; kk < KD; ++kk) {
@@ -369,7 +373,7 @@ __device__ __forceinline__ void decode_slab(const Tile& tile, const uint32_t (&q
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int kpos = k0 + nt * 8 + 2 * (lane & 3) + (e & 1);
-            const float v = (kpos < hi && kpos >= lo) ? s[nt][e] * scale2 : -INFINITY;
+            const float v = (kpos < run.hi && kpos >= run.lo && !in_gap(run, kpos)) ? s[nt][e] * scale2 : -INFINITY;
             s[nt][e] = v;
             tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
         }
@@ -461,7 +465,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
                        const int* __restrict__ req_slot, const int* __restrict__ block_table, int table_width,
                        const int* __restrict__ dec_req, const int* __restrict__ q_start, const int* __restrict__ ctx_len,
                        float* __restrict__ partial, float* __restrict__ stats, int hq, int hkv, int page_size,
-                       float scale, int window, int split_size, int n_splits, int row0) {
+                       float scale, int window, int keep_first, int split_size, int n_splits, int row0) {
     CISR_TRACE_SCOPE(TRACE_ATTN_DECODE_GATHER);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                    // [16][LDS]
@@ -482,9 +486,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int* table = block_table + (size_t)req_slot[req] * table_width;
 
-    int lo = split * split_size;
-    const int hi = min(lo + split_size, ctx);
-    if (window > 0) lo = max(lo, ctx - window);
+    const KeyRun run = decode_key_run(split, split_size, ctx, window, keep_first);
+    const int lo = run.lo, hi = run.hi;
     const size_t part_base = ((size_t)slot * hq + (size_t)kvh * group + row0) * n_splits;
     if (lo >= hi) {      // nothing in this range (the same for every thread): the merge skips a zero denominator
         pdl_wait();
@@ -555,7 +558,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_ca
                 ldmatrix_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
         }
         const bf16* Kt = pipe + (t % STAGES) * 2 * BN * LDS;
-        decode_slab(PaddedTile{Kt, Kt + BN * LDS}, qf, o, m_run, l_run, lo + t * BN + warp * 16, lo, hi, scale2, warp, lane);
+        decode_slab(PaddedTile{Kt, Kt + BN * LDS}, qf, o, m_run, l_run, lo + t * BN + warp * 16, run, scale2, warp, lane);
     }
     cp_async_wait<0>();
     __syncthreads();          // every warp is done with the pipeline buffers: they become the merge area
@@ -632,8 +635,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const bf16* __restrict__ v_cache, int cache_rows, const int* __restrict__ req_slot,
                        const int* __restrict__ block_table, int table_width, const int* __restrict__ dec_req,
                        const int* __restrict__ q_start, const int* __restrict__ ctx_len, float* __restrict__ partial,
-                       float* __restrict__ stats, int hq, int hkv, int page_size, float scale, int window, int split_size,
-                       int cluster, int n_parts, int row0, int* __restrict__ error) {
+                       float* __restrict__ stats, int hq, int hkv, int page_size, float scale, int window, int keep_first,
+                       int split_size, int cluster, int n_parts, int row0, int* __restrict__ error) {
     CISR_TRACE_SCOPE(TRACE_ATTN_DECODE_TMA);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024-byte aligned
@@ -655,9 +658,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int* table = block_table + (size_t)req_slot[req] * table_width;
 
-    int lo = split * split_size;                                     // a multiple of TK (checked by the launcher)
-    const int hi = min(lo + split_size, ctx);
-    if (window > 0) lo = max(lo, ctx - window);
+    const KeyRun run = decode_key_run(split, split_size, ctx, window, keep_first);      // ranges start on multiples of TK (checked by the launcher)
+    const int lo = run.lo, hi = run.hi;
     const size_t part_base = ((size_t)slot * hq + (size_t)kvh * group + row0) * n_parts;
     const bool empty = lo >= hi;              // nothing in this range (the same for every thread)
     if (empty && cluster == 1) {              // the merge skips a zero denominator
@@ -787,7 +789,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
             }
         }
-        const bool edge = k0 < lo || k0 + TK > hi;                   // the same for the whole warp
+        const bool edge = k0 < lo || k0 + TK > hi || (k0 < run.gap_hi && k0 + TK > run.gap_lo);   // the same for the whole warp
         float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < TKT; ++nt) {
@@ -796,7 +798,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 float v = s[nt][e] * scale2;
                 if (edge) {
                     const int kpos = k0 + nt * 8 + 2 * (lane & 3) + (e & 1);
-                    if (kpos >= hi || kpos < lo) v = -INFINITY;
+                    if (kpos >= hi || kpos < lo || in_gap(run, kpos)) v = -INFINITY;
                 }
                 s[nt][e] = v;
                 tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
@@ -969,7 +971,7 @@ CISR_EXPORT int cisr_attn_prefill(const void* q, void* out, const void* k_cache,
                                   const int* req_slot, const int* block_table, int table_width, const int* tile_req,
                                   const int* tile_q0, int n_tiles, const int* q_start, const int* q_len,
                                   const int* ctx_len, int hq, int hkv, int page_size, float scale, int window,
-                                  float sink, void* stream) {
+                                  int keep_first, float sink, void* stream) {
     if (n_tiles <= 0) return 0;
     if (hq % hkv) return -2;
     const size_t smem = PREFILL_SMEM + sizeof(int) * ((size_t)table_width + 4);    // a tile's key range spans at most the table
@@ -982,13 +984,13 @@ CISR_EXPORT int cisr_attn_prefill(const void* q, void* out, const void* k_cache,
     }
     return launch_kernel(attn_prefill_mma_kernel, dim3(n_tiles, hq), dim3(PREFILL_THREADS), smem, (cudaStream_t)stream, g_pdl,
                          (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, req_slot, block_table,
-                         table_width, tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, sink);
+                         table_width, tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, keep_first, sink);
 }
 
 CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
                                  const int* req_slot, const int* block_table, int table_width, const int* dec_req,
                                  int n_dec, const int* q_start, const int* ctx_len, float* partial, float* stats, int hq,
-                                 int hkv, int page_size, float scale, int window, int split_size, int n_splits,
+                                 int hkv, int page_size, float scale, int window, int keep_first, int split_size, int n_splits,
                                  int merge, float sink, void* stream) {
     // merge == 0: the ranges' partial sums and statistics are left in `partial` and `stats` for the caller's own merge
     // (merge_proj.cu merges them in the prologue of the output projection); `out` is then not written.
@@ -1008,7 +1010,7 @@ CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, 
         int status = launch_kernel(attn_decode_mma_kernel, dim3(n_dec, hkv, n_splits), dim3(DEC_THREADS), smem, s, g_pdl,
                                    (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, req_slot, block_table,
                                    table_width, dec_req, q_start, ctx_len, partial, stats, hq, hkv, page_size, scale,
-                                   window, split_size, n_splits, row0);
+                                   window, keep_first, split_size, n_splits, row0);
         if (status) return status;
     }
     if (!merge) return 0;
@@ -1042,7 +1044,7 @@ CISR_EXPORT int cisr_attn_tma_init(int* error_flag) {
 CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cache, const void* v_cache, int n_pages,
                                      const int* req_slot, const int* block_table, int table_width, const int* dec_req,
                                      int n_dec, const int* q_start, const int* ctx_len, float* partial, float* stats,
-                                     int hq, int hkv, int page_size, float scale, int window, int split_size,
+                                     int hq, int hkv, int page_size, float scale, int window, int keep_first, int split_size,
                                      int n_splits, int merge, float sink, void* stream) {
     // `sink` (-inf: none) is added to the denominator by the merge kernel, so the ranges are never merged inside a cluster then
     if (n_dec <= 0) return 0;
@@ -1110,13 +1112,13 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
             status = launch_kernel_cluster(attn_decode_tma_kernel<2>, dim3(n_dec, hkv, n_splits), dim3(DEC_THREADS), smem_deep, s, g_pdl, 1,
                                            map_k, map_v, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                            (int)cache_rows, req_slot, block_table, table_width,
-                                           dec_req, q_start, ctx_len, partial, stats, hq, hkv, page_size, scale, window, split_size,
+                                           dec_req, q_start, ctx_len, partial, stats, hq, hkv, page_size, scale, window, keep_first, split_size,
                                            1, n_parts, row0, g_error);
         else
             status = launch_kernel_cluster(attn_decode_tma_kernel<1>, dim3(n_dec, hkv, n_splits), dim3(DEC_THREADS), smem, s, g_pdl, cluster,
                                            map_k, map_v, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                            (int)cache_rows, req_slot, block_table, table_width,
-                                           dec_req, q_start, ctx_len, partial, stats, hq, hkv, page_size, scale, window, split_size,
+                                           dec_req, q_start, ctx_len, partial, stats, hq, hkv, page_size, scale, window, keep_first, split_size,
                                            cluster, n_parts, row0, g_error);
         if (status) return status;
     }

@@ -61,5 +61,6 @@ int cisr_attn_decode_static(const void* q, void* out, const void* k_cache, const
     float* partial = g_scratch_address[device];       // [n_dec, hq, n_splits, D]
     float* stats = partial + cells * D;                // [n_dec, hq, n_splits, 2]
     return cisr_attn_decode(q, out, k_cache, v_cache, req_slot, block_table, table_width, dec_req, n_dec, q_start,
-                            ctx_len, partial, stats, hq, hkv, page_size, scale, window, split_size, n_splits, -INFINITY /* no sink */, stream);
+                            ctx_len, partial, stats, hq, hkv, page_size, scale, window, 0 /* no kept first keys */, split_size, n_splits,
+                            -INFINITY /* no sink */, stream);
 }

@@ -79,7 +79,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ tile_req, const int* __restrict__ tile_q0,
                             const int* __restrict__ q_start, const int* __restrict__ q_len,
                             const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window,
-                            float sink, int* __restrict__ error) {
+                            int keep_first, float sink, int* __restrict__ error) {
     CISR_TRACE_SCOPE(TRACE_ATTN_PREFILL);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -116,7 +116,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     const int k_end = qpos0 + rows;                                                       // the last row sees keys up to its own position
     const int k_begin = ((window > 0 ? max(0, qpos0 - window + 1) : 0) / BN) * BN;
-    const int n_tiles = (k_end - k_begin + BN - 1) / BN;
+    // key tiles: those that hold kept first keys (keys below keep_first stay in sight behind the window), then from the
+    // window's first tile on; the two runs never overlap
+    const int n_kept = (window > 0 && keep_first > 0) ? min((keep_first + BN - 1) / BN, k_begin / BN) : 0;
+    const int n_tiles = n_kept + (k_end - k_begin + BN - 1) / BN;
+    auto tile_k0 = [&](int j) { return j < n_kept ? j * BN : k_begin + (j - n_kept) * BN; };
     if (tid == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < K_STAGES; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
@@ -176,7 +180,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             __syncwarp();
             for (int b = lane; b < NSUB * boxes; b += 32) {       // lane b: box b (64-column half, run of box_rows keys)
                 const int i = b % boxes, sub = b / boxes;
-                const int kpos = k_begin + j * BN + i * box_rows;
+                const int kpos = tile_k0(j) + i * box_rows;
                 const int page = kpos < k_end ? __ldg(table + kpos / page_size) : -1;     // the table is older than the kernel before
                 const int row = page < 0 ? cache_rows : (page * hkv + kvh) * page_size + kpos % page_size;   // beyond the cache: zeros
                 tma_load_2d(ring + s * KV_BYTES + sub * KV_SUB + i * box_rows * 128, map, sub * 64, row, full + s);
@@ -250,11 +254,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         auto step = [&](int j) {
             if (ok) ok = __all_sync(0xffffffffu, wait(s_full + (j & 1), (j >> 1) & 1));
             if (!ok) return;
-            const int kt = k_begin + j * BN;                       // the tile's first key
+            const int kt = tile_k0(j);                              // the tile's first key
             const int k0 = kt + group * HALF;                     // this thread's first key
             // tiles on the diagonal, at the window's start and at the end of the keys need the per-element mask
             const bool edge = kt + BN - 1 > qpos0 || kt + BN > k_end || (window > 0 && kt <= qpos0 + BM - 1 - window);
-            auto masked = [&](int kpos) { return kpos > qpos || kpos >= k_end || (window > 0 && kpos <= qpos - window); };
+            auto masked = [&](int kpos) { return kpos > qpos || kpos >= k_end || (window > 0 && kpos <= qpos - window && kpos >= keep_first); };
             const uint32_t s_addr = tmem_base + lane_base + (uint32_t)((j & 1) * BN + group * HALF);
             auto fetch = [&]() {
 #pragma unroll
@@ -422,7 +426,7 @@ CISR_EXPORT int cisr_attn_prefill_tcgen05(const void* q, void* out, int n_tokens
                                           int n_pages, const int* req_slot, const int* block_table, int table_width,
                                           const int* tile_req, const int* tile_q0, int n_tiles, const int* q_start,
                                           const int* q_len, const int* ctx_len, int hq, int hkv, int page_size, float scale,
-                                          int window, float sink, void* stream) {
+                                          int window, int keep_first, float sink, void* stream) {
     if (n_tiles <= 0) return 0;
     if (!g_encode || !g_error) return -13;
     if (hq % hkv || !cisr_attn_tcgen05_ok(page_size)) return -2;
@@ -444,5 +448,5 @@ CISR_EXPORT int cisr_attn_prefill_tcgen05(const void* q, void* out, int n_tokens
     }
     return launch_kernel(attn_prefill_tcgen05_kernel, dim3(n_tiles, hq), dim3(THREADS), smem, (cudaStream_t)stream, g_pdl, map_q,
                          map_k, map_v, (bf16*)out, (int)cache_rows, req_slot, block_table, table_width, tile_req, tile_q0,
-                         q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, sink, g_error);
+                         q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, keep_first, sink, g_error);
 }

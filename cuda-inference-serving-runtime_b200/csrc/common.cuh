@@ -20,6 +20,30 @@ template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// Which keys a single new token (position ctx - 1) sees inside key range [split * split_size, (split + 1) * split_size):
+// the range's part of the window [ctx - window, ctx) (window <= 0: every key) and its part of the sequence's first
+// `keep_first` keys, which stay in sight whatever the distance.  The kernels walk ONE run [lo, hi); where the range
+// holds kept keys and window keys with others between them, those are [gap_lo, gap_hi) and get masked (else the gap
+// is empty).  A run that is not empty starts with a key in sight.
+struct KeyRun { int lo, hi, gap_lo, gap_hi; };
+__device__ __forceinline__ KeyRun decode_key_run(int split, int split_size, int ctx, int window, int keep_first) {
+    KeyRun r;
+    r.lo = split * split_size;
+    r.hi = min(r.lo + split_size, ctx);
+    r.gap_lo = r.gap_hi = 0;
+    if (window > 0) {
+        const int w0 = ctx - window;
+        if (keep_first > 0 && r.lo < keep_first) {
+            if (w0 >= r.hi) r.hi = min(r.hi, keep_first);
+            else if (w0 > keep_first) { r.gap_lo = keep_first; r.gap_hi = w0; }
+        } else {
+            r.lo = max(r.lo, w0);
+        }
+    }
+    return r;
+}
+__device__ __forceinline__ bool in_gap(const KeyRun& r, int kpos) { return kpos >= r.gap_lo && kpos < r.gap_hi; }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -1,11 +1,16 @@
 // Routed experts: a router that scores every expert per token, picks a few, and the chosen experts' small
 // feed-forward layers, summed with the router's weights.
 //
-//   scores s = sigmoid(W_router h)                       (float sums and float arithmetic whatever the storage type)
+//   scores s = sigmoid(W_router h), or softmax(W_router h) over all router outputs
+//                                                        (float sums and float arithmetic whatever the storage type)
+//   a choice bias (one number per router output, may be absent) is added to the scores for the choice only
 //   experts form n_groups equal groups of neighbours; a group's score is the sum of its two best members; only members
 //   of the `keep` best groups can be chosen (n_groups 0: all can)
 //   the `top` best open experts are chosen, weight = s * route_scale (not renormalised)
-//   y = sum over chosen e of weight_e * W_down_e act(W_up_e h),   act(z) = max(z, 0)^2
+//   y = sum over chosen e of weight_e * W_down_e act(W_up_e h),   act(z) = max(z, 0)^2, or the gated form
+//       act = g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit), where W_up_e stacks the
+//       gate rows on the up rows ([2 ff, hidden]) and alpha = 1.702
+//   router outputs beyond the experts that have matrices are identity experts: their output is the token's input h
 //
 // Two shapes of the expert products.  Few tokens (and the float path): a warp per output feature, each chosen expert's
 // rows streamed once per token that chose it (moe_up_rows / moe_down_rows).  Many tokens in bfloat16: the pairs are
@@ -57,31 +62,43 @@ __device__ __forceinline__ float warp_dot(const __nv_bfloat16* __restrict__ a, c
 // The logits z = W_router h come from the engine's matrix products (float sums of bfloat16 or float operands).  A warp
 // per token: its lanes turn the logits into scores and score the groups, then keep the best groups and take the best
 // open experts one after the other (ties go to the lower index).  Shared memory per warp: n_experts scores,
-// n_experts flags, n_groups group scores.
+// n_experts flags, n_experts ranks, n_groups group scores.
 constexpr int SELECT_WARPS = 4;
 __global__ void __launch_bounds__(32 * SELECT_WARPS)
 moe_select_kernel(const float* __restrict__ logits, int tokens, int n_experts, int top, int n_groups, int keep, float route_scale,
-                  int* __restrict__ chosen, float* __restrict__ weight) {
+                  int softmax, const float* __restrict__ choice_bias, int* __restrict__ chosen, float* __restrict__ weight) {
     extern __shared__ float select_smem[];
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, t = blockIdx.x * SELECT_WARPS + warp;
     if (t >= tokens) return;
-    const int per_warp = 2 * n_experts + n_groups;
-    float* score = select_smem + (size_t)warp * per_warp;
+    const int per_warp = 3 * n_experts + n_groups;
+    float* score = select_smem + (size_t)warp * per_warp;       // what the weights are made of
     int* open_ = reinterpret_cast<int*>(score + n_experts);
-    float* group_score = score + 2 * n_experts;
+    float* rank = score + 2 * n_experts;                        // what the choice goes by: the score plus the choice bias
+    float* group_score = score + 3 * n_experts;
+    const float* z = logits + (size_t)t * n_experts;
+    float z_max = -INFINITY, z_sum = 1.f;
+    if (softmax) {
+        for (int e = lane; e < n_experts; e += 32) z_max = fmaxf(z_max, z[e]);
+        z_max = warp_max(z_max);
+        z_sum = 0.f;
+        for (int e = lane; e < n_experts; e += 32) z_sum += expf(z[e] - z_max);
+        z_sum = warp_sum(z_sum);
+    }
     for (int e = lane; e < n_experts; e += 32) {
-        score[e] = 1.f / (1.f + expf(-logits[(size_t)t * n_experts + e]));
+        const float sc = softmax ? expf(z[e] - z_max) / z_sum : 1.f / (1.f + expf(-z[e]));
+        score[e] = sc;
+        rank[e] = choice_bias ? sc + choice_bias[e] : sc;
         open_[e] = n_groups > 0 ? 0 : 1;
     }
     __syncwarp();
     if (n_groups > 0) {
         const int per = n_experts / n_groups;
         for (int g = lane; g < n_groups; g += 32) {
-            float best = -1.f, second = -1.f;
+            float best = -INFINITY, second = -INFINITY;
             for (int i = 0; i < per; ++i) {
-                const float s = score[g * per + i];
+                const float s = rank[g * per + i];
                 if (s > best) { second = best; best = s; }
                 else if (s > second) second = s;
             }
@@ -92,7 +109,7 @@ moe_select_kernel(const float* __restrict__ logits, int tokens, int n_experts, i
     // The best of the warp's candidates: each lane looks at every 32nd, then the lanes compare (the larger score wins, the
     // lower index among equals), so every round costs a few shuffles instead of a walk over all experts by one lane.
     auto warp_best = [&](const float* value, const int* allowed, int n, float& best_value) {
-        float bv = -1.f; int bi = 0x7fffffff;
+        float bv = -INFINITY; int bi = 0x7fffffff;
         for (int i = lane; i < n; i += 32)
             if ((!allowed || allowed[i]) && value[i] > bv) { bv = value[i]; bi = i; }
 #pragma unroll
@@ -111,14 +128,14 @@ moe_select_kernel(const float* __restrict__ logits, int tokens, int n_experts, i
             const int best = warp_best(group_score, nullptr, n_groups, v);
             if (best == 0x7fffffff) break;
             __syncwarp();
-            if (lane == 0) group_score[best] = -2.f;                 // below every score and below the "nothing found" mark
+            if (lane == 0) group_score[best] = -INFINITY;            // never the best again ("nothing found" compares > -inf)
             for (int i = lane; i < per; i += 32) open_[best * per + i] = 1;
             __syncwarp();
         }
     }
     for (int k = 0; k < top; ++k) {
         float v;
-        int best = warp_best(score, open_, n_experts, v);
+        int best = warp_best(rank, open_, n_experts, v);
         __syncwarp();
         if (lane == 0) {
             if (best == 0x7fffffff) best = 0;                        // fewer open experts than `top`: the host refuses such a configuration
@@ -131,30 +148,42 @@ moe_select_kernel(const float* __restrict__ logits, int tokens, int n_experts, i
 }
 
 CISR_EXPORT int cisr_moe_select(const float* logits, int tokens, int n_experts, int top, int n_groups, int keep, float route_scale,
-                                int* chosen, float* weight, void* stream) {
+                                int softmax, const float* choice_bias, int* chosen, float* weight, void* stream) {
     if (tokens <= 0) return 0;
     if (n_experts <= 0 || top <= 0 || top > n_experts || (n_groups > 0 && (n_experts % n_groups || keep <= 0 || keep > n_groups)))
         return -2;
-    const size_t smem = (size_t)SELECT_WARPS * (2 * n_experts + (n_groups > 0 ? n_groups : 0)) * sizeof(float);
+    const size_t smem = (size_t)SELECT_WARPS * (3 * n_experts + (n_groups > 0 ? n_groups : 0)) * sizeof(float);
     if (smem > 48 * 1024) return -3;
     return launch_kernel(moe_select_kernel, dim3((tokens + SELECT_WARPS - 1) / SELECT_WARPS), dim3(32 * SELECT_WARPS), smem,
-                         (cudaStream_t)stream, g_pdl, logits, tokens, n_experts, top, n_groups > 0 ? n_groups : 0, keep, route_scale, chosen,
-                         weight);
+                         (cudaStream_t)stream, g_pdl, logits, tokens, n_experts, top, n_groups > 0 ? n_groups : 0, keep, route_scale, softmax,
+                         choice_bias, chosen, weight);
 }
 
 // ---------------------------------------------------------------- few tokens: a warp per output feature
-// act[t * top + k, f] = max(W_up[e][f] . h[t], 0)^2 with e = chosen[t, k];   W_up [experts, ff, hidden].
+// act[t * top + k, f] = max(W_up[e][f] . h[t], 0)^2 with e = chosen[t, k];   W_up [experts, ff, hidden].  gated: W_up
+// [experts, 2 ff, hidden] (gate rows, then up rows) and act = g' sigmoid(alpha g') (u' + 1), g and u clamped by `limit`.
+// Pairs whose expert has no matrices (e >= n_real: an identity expert) are skipped.
 constexpr int ROW_WARPS = 8;
+constexpr float GATE_ALPHA = 1.702f;
 template <typename T>
 __global__ void __launch_bounds__(32 * ROW_WARPS)
 moe_up_rows_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __restrict__ chosen, int hidden, int ff,
-                   int top, T* __restrict__ act) {
+                   int top, int n_real, int gated, float limit, T* __restrict__ act) {
     pdl_trigger();
     pdl_wait();
     const int pair = blockIdx.x, lane = threadIdx.x & 31, f = blockIdx.y * ROW_WARPS + (threadIdx.x >> 5);
     if (f >= ff) return;
     const int e = chosen[pair];
-    const float z = warp_dot(w_up + ((size_t)e * ff + f) * hidden, h + (size_t)(pair / top) * hidden, hidden, lane);
+    if (e >= n_real) return;
+    const T* x = h + (size_t)(pair / top) * hidden;
+    if (gated) {
+        const T* w = w_up + (size_t)e * 2 * ff * hidden;
+        const float g = fminf(warp_dot(w + (size_t)f * hidden, x, hidden, lane), limit);
+        const float u = fminf(fmaxf(warp_dot(w + (size_t)(ff + f) * hidden, x, hidden, lane), -limit), limit);
+        if (lane == 0) act[(size_t)pair * ff + f] = from_float<T>(g / (1.f + expf(-GATE_ALPHA * g)) * (u + 1.f));
+        return;
+    }
+    const float z = warp_dot(w_up + ((size_t)e * ff + f) * hidden, x, hidden, lane);
     if (lane == 0) { const float r = fmaxf(z, 0.f); act[(size_t)pair * ff + f] = from_float<T>(r * r); }
 }
 
@@ -163,8 +192,8 @@ moe_up_rows_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const in
 template <typename T>
 __global__ void __launch_bounds__(32 * ROW_WARPS)
 moe_down_rows_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int* __restrict__ chosen,
-                     const float* __restrict__ weight, int hidden, int ff, int top, const float* __restrict__ out_scale,
-                     float* __restrict__ out) {
+                     const float* __restrict__ weight, int hidden, int ff, int top, int n_real, const T* __restrict__ h,
+                     const float* __restrict__ out_scale, float* __restrict__ out) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x, lane = threadIdx.x & 31, c = blockIdx.y * ROW_WARPS + (threadIdx.x >> 5);
@@ -172,30 +201,32 @@ moe_down_rows_kernel(const T* __restrict__ act, const T* __restrict__ w_down, co
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {
         const int e = chosen[(size_t)t * top + k];
+        if (e >= n_real) { acc += weight[(size_t)t * top + k] * to_float(h[(size_t)t * hidden + c]); continue; }     // an identity expert
         acc += weight[(size_t)t * top + k] * warp_dot(w_down + ((size_t)e * hidden + c) * ff, act + ((size_t)t * top + k) * ff, ff, lane);
     }
     if (lane == 0) out[(size_t)t * hidden + c] = out_scale ? acc * out_scale[c] : acc;
 }
 
 CISR_EXPORT int cisr_moe_rows(const void* h, const void* w_up, const void* w_down, int dtype, const int* chosen,
-                              const float* weight, int tokens, int hidden, int ff, int top, void* act, const float* out_scale,
-                              float* out, void* stream) {
+                              const float* weight, int tokens, int hidden, int ff, int top, int n_real, int gated, float limit,
+                              void* act, const float* out_scale, float* out, void* stream) {
     if (tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 up_grid(tokens * top, (ff + ROW_WARPS - 1) / ROW_WARPS), down_grid(tokens, (hidden + ROW_WARPS - 1) / ROW_WARPS);
     int st;
     if (dtype == CISR_BF16) {
         st = launch_kernel(moe_up_rows_kernel<__nv_bfloat16>, up_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl, (const __nv_bfloat16*)h,
-                           (const __nv_bfloat16*)w_up, chosen, hidden, ff, top, (__nv_bfloat16*)act);
+                           (const __nv_bfloat16*)w_up, chosen, hidden, ff, top, n_real, gated, limit, (__nv_bfloat16*)act);
         if (st) return st;
         return launch_kernel(moe_down_rows_kernel<__nv_bfloat16>, down_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl,
-                             (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, chosen, weight, hidden, ff, top, out_scale, out);
+                             (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, chosen, weight, hidden, ff, top, n_real,
+                             (const __nv_bfloat16*)h, out_scale, out);
     }
     st = launch_kernel(moe_up_rows_kernel<float>, up_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl, (const float*)h, (const float*)w_up,
-                       chosen, hidden, ff, top, (float*)act);
+                       chosen, hidden, ff, top, n_real, gated, limit, (float*)act);
     if (st) return st;
     return launch_kernel(moe_down_rows_kernel<float>, down_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl, (const float*)act,
-                         (const float*)w_down, chosen, weight, hidden, ff, top, out_scale, out);
+                         (const float*)w_down, chosen, weight, hidden, ff, top, n_real, (const float*)h, out_scale, out);
 }
 
 // ---------------------------------------------------------------- many tokens: rows sorted by expert
@@ -204,6 +235,7 @@ CISR_EXPORT int cisr_moe_rows(const void* h, const void* w_up, const void* w_dow
 //   row_of[pair]        the row of pair t * top + k in the sorted layout
 //   src_token[row]      the token whose activations row `row` holds, -1 for padding (and for rows beyond the last tile used)
 //   tile_group[i]       the expert of row tile i, -1 for tiles beyond the last one used
+// Pairs whose expert has no matrices (chosen >= n_experts: an identity expert) get row_of = -1 and no row.
 // One CTA; shared memory: 3 * n_experts ints.  Which row inside its expert's block a pair gets depends on the order the
 // atomics happen to run in; every row is computed by itself and a token's experts are summed in the router's order, so
 // the result does not.
@@ -219,7 +251,8 @@ __global__ void moe_sort_kernel(const int* __restrict__ chosen, int n_pairs, int
     for (int r = threadIdx.x; r < max_rows; r += blockDim.x) src_token[r] = -1;
     for (int i = threadIdx.x; i < max_rows / tile; i += blockDim.x) tile_group[i] = -1;
     __syncthreads();
-    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&count[chosen[p]], 1);
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x)
+        if (chosen[p] < n_experts) atomicAdd(&count[chosen[p]], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0;
@@ -230,6 +263,7 @@ __global__ void moe_sort_kernel(const int* __restrict__ chosen, int n_pairs, int
         for (int i = offset[e] / tile; i < (offset[e] + count[e] + tile - 1) / tile; ++i) tile_group[i] = e;
     for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
         const int e = chosen[p];
+        if (e >= n_experts) { row_of[p] = -1; continue; }
         const int row = offset[e] + atomicAdd(&fill[e], 1);
         row_of[p] = row;
         src_token[row] = p / top;
@@ -245,15 +279,20 @@ __global__ void moe_gather_kernel(const uint4* __restrict__ h, const int* __rest
         sorted[(size_t)row * row_vec + i] = src >= 0 ? h[(size_t)src * row_vec + i] : make_uint4(0, 0, 0, 0);
 }
 
-// out[t, c] = out_scale[c] * sum_k weight[t, k] * sorted_out[row_of[t * top + k], c], k in the router's order (out_scale null: 1).
+// out[t, c] = out_scale[c] * sum_k weight[t, k] * sorted_out[row_of[t * top + k], c], k in the router's order (out_scale null: 1);
+// a pair without a row (row_of < 0: an identity expert) adds weight * h[t, c].
 __global__ void moe_combine_kernel(const float* __restrict__ sorted_out, const int* __restrict__ row_of, const float* __restrict__ weight,
-                                   int top, int hidden, const float* __restrict__ out_scale, float* __restrict__ out) {
+                                   int top, int hidden, const __nv_bfloat16* __restrict__ h, const float* __restrict__ out_scale,
+                                   float* __restrict__ out) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         float acc = 0.f;
-        for (int k = 0; k < top; ++k) acc += weight[(size_t)t * top + k] * sorted_out[(size_t)row_of[(size_t)t * top + k] * hidden + c];
+        for (int k = 0; k < top; ++k) {
+            const int row = row_of[(size_t)t * top + k];
+            acc += weight[(size_t)t * top + k] * (row >= 0 ? sorted_out[(size_t)row * hidden + c] : to_float(h[(size_t)t * hidden + c]));
+        }
         out[(size_t)t * hidden + c] = out_scale ? acc * out_scale[c] : acc;
     }
 }
@@ -278,8 +317,8 @@ CISR_EXPORT int cisr_moe_gather(const void* h, const int* src_token, void* sorte
 }
 
 CISR_EXPORT int cisr_moe_combine(const float* sorted_out, const int* row_of, const float* weight, int tokens, int top, int hidden,
-                                 const float* out_scale, float* out, void* stream) {
+                                 const void* h, const float* out_scale, float* out, void* stream) {
     if (tokens <= 0) return 0;
     return launch_kernel(moe_combine_kernel, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, g_pdl, sorted_out, row_of, weight, top,
-                         hidden, out_scale, out);
+                         hidden, (const __nv_bfloat16*)h, out_scale, out);
 }

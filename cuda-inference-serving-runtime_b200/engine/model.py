@@ -121,9 +121,14 @@ class Model:
                 uses.append(self.layers[entry.layer].mixer.cache_use())
         return uses
 
+    def side_states(self) -> list:
+        """Per run entry: the fixed-size state its mixer keeps besides its pages (None: none).  Always the entry's own,
+        also where the entry reads another entry's pages."""
+        return [getattr(self.layers[entry.layer].mixer, "side_state", lambda: None)() for entry in self.spec.run]
+
     def make_cache(self, n_pages: int, page_size: int = 16, max_slots: int = 64) -> CacheManager:
         return CacheManager(self.cache_uses(), n_pages, page_size, max_slots, self.spec.max_positions,
-                            dtype=self.dtype, device=self.device)
+                            dtype=self.dtype, device=self.device, side_states=self.side_states())
 
     # ---------------------------------------------------------------- forward
     def step_beginners(self) -> list:

@@ -346,9 +346,9 @@ def _sink(sink: Optional[float]) -> ctypes.c_float:
 
 
 def attn_prefill_wide(q, out, k_cache, v_cache, req_slot, block_table, wide_req, wide_q0, q_start, q_len, ctx_len, hq, hkv,
-                      page_size, scale, window, sink: Optional[float] = None) -> None:
+                      page_size, scale, window, sink: Optional[float] = None, keep_first: int = 0) -> None:
     """Attention of portions on tcgen05: q, out [tokens, hq, D]; tiles of 128 queries as (request, first query).
-    `sink`: see `_sink`."""
+    `sink`: see `_sink`.  `keep_first`: the sequence's first keys that stay in sight behind a window."""
     dim = k_cache.shape[-1]
     _need(q, torch.bfloat16, "q", 3); _need(out, torch.bfloat16, "out", 3); _need(k_cache, torch.bfloat16, "k_cache", 4)
     _need(v_cache, torch.bfloat16, "v_cache", 4)
@@ -361,15 +361,16 @@ def attn_prefill_wide(q, out, k_cache, v_cache, req_slot, block_table, wide_req,
     _check(lib.cisr_attn_prefill_tcgen05(_p(q), _p(out), q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0], _p(req_slot),
                                          _p(block_table), block_table.shape[1], _p(wide_req), _p(wide_q0), wide_req.numel(),
                                          _p(q_start), _p(q_len), _p(ctx_len), hq, hkv, page_size, ctypes.c_float(scale),
-                                         int(window or 0), _sink(sink), _stream()), "attn_prefill_wide")
+                                         int(window or 0), int(keep_first or 0), _sink(sink), _stream()), "attn_prefill_wide")
 
 
 PREFILL_TILE = 64
 
 
 def attn_prefill(q, out, k_cache, v_cache, req_slot, block_table, tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv,
-                 page_size, scale, window, kind: str = "auto", sink: Optional[float] = None) -> None:
-    """Attention of portions: q, out [tokens, hq, D]; tiles list (request, first query of the tile)."""
+                 page_size, scale, window, kind: str = "auto", sink: Optional[float] = None, keep_first: int = 0) -> None:
+    """Attention of portions: q, out [tokens, hq, D]; tiles list (request, first query of the tile).  Query i sees key
+    j <= i when window is None or i - j < window or j < keep_first."""
     dim = k_cache.shape[-1]
     _need(q, k_cache.dtype, "q"); _need(out, k_cache.dtype, "out"); _need(k_cache, None, "k_cache", 4)
     _need(v_cache, k_cache.dtype, "v_cache", 4)
@@ -379,13 +380,15 @@ def attn_prefill(q, out, k_cache, v_cache, req_slot, block_table, tile_req, tile
     lib = attention_library(dim, k_cache.dtype, kind)
     _check(lib.cisr_attn_prefill(_p(q), _p(out), _p(k_cache), _p(v_cache), _p(req_slot), _p(block_table), block_table.shape[1],
                                  _p(tile_req), _p(tile_q0), tile_req.numel(), _p(q_start), _p(q_len), _p(ctx_len),
-                                 hq, hkv, page_size, ctypes.c_float(scale), int(window or 0), _sink(sink), _stream()), "attn_prefill")
+                                 hq, hkv, page_size, ctypes.c_float(scale), int(window or 0), int(keep_first or 0), _sink(sink),
+                                 _stream()), "attn_prefill")
 
 
 def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec, q_start, ctx_len, partial, stats, hq, hkv,
                 page_size, scale, window, split_size, n_splits, kind: str = "auto", staging: str = "auto", merge: bool = True,
-                sink: Optional[float] = None) -> None:
-    """Attention of single new tokens, split over key ranges of `split_size`, merged into out.
+                sink: Optional[float] = None, keep_first: int = 0) -> None:
+    """Attention of single new tokens, split over key ranges of `split_size`, merged into out.  `keep_first`: the
+    sequence's first keys that stay in sight behind a window.
 
     `merge=False` (tensor-core kernels only) leaves the ranges' partial sums in `partial` and `stats` and does not write
     `out`: the caller merges them itself (`merge_out_proj`).
@@ -402,7 +405,7 @@ def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec,
         raise KernelError("attn_decode: scratch for partial sums is too small")
     lib = attention_library(dim, k_cache.dtype, kind)
     tail = [_p(req_slot), _p(block_table), block_table.shape[1], _p(dec_req), n_dec, _p(q_start), _p(ctx_len), _p(partial),
-            _p(stats), hq, hkv, page_size, ctypes.c_float(scale), int(window or 0), split_size, n_splits]
+            _p(stats), hq, hkv, page_size, ctypes.c_float(scale), int(window or 0), int(keep_first or 0), split_size, n_splits]
     if lib._tensor_core:
         tail.append(int(merge))
     elif not merge:
@@ -547,6 +550,172 @@ def hyper_sum(streams: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     if out.shape != (tokens, hidden):
         raise KernelError("hyper_sum: out must be [tokens, hidden]")
     _check(_hyper().cisr_hyper_sum(_p(streams), _p(out), tokens, n_streams, hidden, _stream()), "hyper_sum")
+    return out
+
+
+# ------------------------------------------------------------------ differential attention: row kernels around the paged attention
+_diff_state = {}
+
+
+def _diff():
+    lib = _diff_state.get("lib")
+    if lib is None:
+        lib = load_library("diff_attention.cu")
+        for name in ("cisr_diff_rows", "cisr_conv_keep", "cisr_diff_combine"):
+            getattr(lib, name).restype = ctypes.c_int
+        lib.cisr_diff_set_pdl(int(_pdl_state["on"]))
+        _diff_state["lib"] = lib
+    return lib
+
+
+def diff_jobs():
+    return [("diff_attention.cu", {}, ())]
+
+
+def diff_rows(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, state: torch.Tensor, *, token_req, req_slot, q_start, positions,
+              q_out: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], block_table, page_size: int,
+              hq: int, hkv: int, key_dim: int, value_dim: int) -> None:
+    """Per token of a step: the causal convolution over time (taps weights per channel, conv_w float [channels, taps], the
+    last one the current token's; inputs before the portion from `state` [slots, taps - 1, channels], zeros before the
+    sequence) of the first columns of proj (float [tokens, cols]: q [hq * 2 * key_dim], then, when caches are given, k
+    [hkv * 2 * key_dim] and v [hkv * value_dim]); the two maps of head h become query rows 2 h and 2 h + 1 of q_out
+    [tokens, 2 hq, D] (map m at columns [m * key_dim, (m + 1) * key_dim), zeros elsewhere), a key row [k1 | k2 | 0] and a
+    value row [v | 0] go into the token's place in the pages [pages, hkv, page, D]."""
+    _need(proj, torch.float32, "proj", 2); _need(conv_w, torch.float32, "conv_w", 2); _need(state, torch.float32, "state")
+    _need(q_out, None, "q_out", 3)
+    tokens, width = q_out.shape[0], q_out.shape[2]
+    write = k_cache is not None
+    channels = hq * 2 * key_dim + ((hkv * 2 * key_dim + hkv * value_dim) if write else 0)
+    if (proj.shape[0] != tokens or proj.shape[1] < channels or tuple(conv_w.shape) != (channels, taps) or q_out.shape[1] != 2 * hq
+            or state[0].numel() != max(taps - 1, 0) * channels and taps > 1):
+        raise KernelError("diff_rows: shapes disagree")
+    if write:
+        _need(k_cache, q_out.dtype, "k_cache", 4); _need(v_cache, q_out.dtype, "v_cache", 4)
+        if k_cache.shape[1:] != (hkv, page_size, width) or v_cache.shape != k_cache.shape:
+            raise KernelError("diff_rows: the cache is not [pages, kv_heads, page, D]")
+    for name, t in (("token_req", token_req), ("req_slot", req_slot), ("q_start", q_start), ("positions", positions), ("block_table", block_table)):
+        _need(t, torch.int32, name)
+    _check(_diff().cisr_diff_rows(_p(proj), proj.shape[1], _p(conv_w), taps, _p(state), ctypes.c_longlong(state[0].numel()),
+                                  _p(token_req), _p(req_slot), _p(q_start), _p(positions), _p(q_out), _p(k_cache), _p(v_cache),
+                                  dtype_code(q_out.dtype), _p(block_table), block_table.shape[1], page_size, tokens, hq, hkv, key_dim,
+                                  value_dim, width, int(write), _stream()), "diff_rows")
+
+
+def conv_keep(proj: torch.Tensor, state: torch.Tensor, req_slot, q_start, q_len, n_req: int, taps: int, channels: int) -> None:
+    """Per request of a step: the last taps - 1 rows of its portion's first `channels` columns of proj (older ones from
+    what was kept before, where the portion is shorter) become its kept inputs, state [slots, taps - 1, channels]."""
+    if taps <= 1:
+        return
+    _need(proj, torch.float32, "proj", 2); _need(state, torch.float32, "state")
+    _check(_diff().cisr_conv_keep(_p(proj), proj.shape[1], _p(state), ctypes.c_longlong(state[0].numel()), _p(req_slot), _p(q_start),
+                                  _p(q_len), n_req, taps, channels, _stream()), "conv_keep")
+
+
+def diff_combine(mixed: torch.Tensor, gate: torch.Tensor, gate_col: int, out: torch.Tensor, hq: int, value_dim: int, lam: float,
+                 eps: float, out_scale: float) -> torch.Tensor:
+    """Per (token, head): o = a1 - lam * a2 from rows 2 h and 2 h + 1 of mixed [tokens, 2 hq, D] (their first value_dim
+    columns), o / sqrt(mean(o^2) + eps) * out_scale * sigmoid(gate), the gate's logits being columns gate_col + h *
+    value_dim of the float tensor `gate`; out [tokens, hq * value_dim] in mixed's type."""
+    _need(mixed, None, "mixed", 3); _need(gate, torch.float32, "gate", 2); _need(out, mixed.dtype, "out", 2)
+    tokens, _, width = mixed.shape
+    if mixed.shape[1] != 2 * hq or out.shape != (tokens, hq * value_dim) or gate.shape[0] != tokens or gate.shape[1] < gate_col + hq * value_dim:
+        raise KernelError("diff_combine: shapes disagree")
+    _check(_diff().cisr_diff_combine(_p(mixed), _p(gate), gate.shape[1], gate_col, _p(out), dtype_code(mixed.dtype), tokens, hq, value_dim,
+                                     width, ctypes.c_float(lam), ctypes.c_float(eps), ctypes.c_float(out_scale), _stream()), "diff_combine")
+    return out
+
+
+# ------------------------------------------------------------------ depth-weighted average of the residual stream
+_depth_state = {}
+
+
+def _depth():
+    lib = _depth_state.get("lib")
+    if lib is None:
+        lib = load_library("depth.cu")
+        lib.cisr_depth_mix_norm.restype = ctypes.c_int
+        lib.cisr_depth_set_pdl(int(_pdl_state["on"]))
+        _depth_state["lib"] = lib
+    return lib
+
+
+def depth_jobs():
+    return [("depth.cu", {}, ())]
+
+
+def depth_mix_norm(hist: torch.Tensor, x: torch.Tensor, pending: Optional[torch.Tensor], w: torch.Tensor, n_new: int, *,
+                   norm_w: Optional[torch.Tensor] = None, eps: float = 0.0, h: Optional[torch.Tensor] = None,
+                   mixed_out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None, store: bool = True):
+    """The seam between two layers (csrc/depth.cu): entry n_new of hist (float [entries, tokens, hidden]) becomes x +
+    pending, x becomes sum_(j <= n_new) w[j] * hist[j], and h = rmsnorm(x) * norm_w.  `rows` picks tokens (nothing is
+    stored then); `mixed_out` also receives the sum."""
+    _need(hist, torch.float32, "hist", 3); _need(x, torch.float32, "x", 2); _need(w, torch.float32, "w", 1)
+    entries, tokens, hidden = hist.shape
+    if x.shape != (tokens, hidden) or not 1 <= n_new < entries or w.numel() != n_new + 1:
+        raise KernelError("depth_mix_norm: shapes disagree")
+    if pending is not None:
+        _need(pending, torch.float32, "pending", 2)
+        if pending.shape != x.shape:
+            raise KernelError("depth_mix_norm: pending and x differ in shape")
+    n_rows = tokens if rows is None else rows.numel()
+    if rows is not None:
+        _need(rows, torch.int32, "rows", 1)
+        store = False
+    if h is not None:
+        _need(h, None, "h", 2); _need(norm_w, torch.float32, "norm_w", 1)
+        if h.shape != (n_rows, hidden) or norm_w.numel() != hidden:
+            raise KernelError("depth_mix_norm: h or norm_w has the wrong shape")
+    if mixed_out is not None:
+        _need(mixed_out, torch.float32, "mixed_out", 2)
+    _check(_depth().cisr_depth_mix_norm(_p(hist), ctypes.c_longlong(tokens * hidden), _p(x), _p(pending), _p(w), n_new,
+                                        _p(norm_w if h is not None else None), ctypes.c_float(eps), _p(h),
+                                        dtype_code(h.dtype) if h is not None else 0, _p(mixed_out), _p(rows), n_rows, hidden,
+                                        int(bool(store)), _stream()), "depth_mix_norm")
+    return h
+
+
+# ------------------------------------------------------------------ feed-forward row kernels (whole-row and gated activations)
+_ffn_rows_state = {}
+
+
+def _ffn_rows():
+    lib = _ffn_rows_state.get("lib")
+    if lib is None:
+        lib = load_library("ffn_rows.cu")
+        lib.cisr_polynorm.restype = ctypes.c_int
+        lib.cisr_gated_clamp.restype = ctypes.c_int
+        lib.cisr_ffn_rows_set_pdl(int(_pdl_state["on"]))
+        _ffn_rows_state["lib"] = lib
+    return lib
+
+
+def ffn_rows_jobs():
+    return [("ffn_rows.cu", {}, ())]
+
+
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = a N(z_t) + b N(z_t^2) + c N(z_t^3) + e, N(u) = u / sqrt(mean(u^2) + eps) over the row, coef = (a, b, c, e)
+    float; z float [tokens, ff]; out [tokens, >= ff] (further columns zero)."""
+    _need(z, torch.float32, "z", 2); _need(coef, torch.float32, "coef", 1); _need(out, None, "out", 2)
+    if coef.numel() != 4 or out.shape[0] != z.shape[0] or out.shape[1] < z.shape[1]:
+        raise KernelError("polynorm: shapes disagree")
+    _check(_ffn_rows().cisr_polynorm(_p(z), z.shape[1], _p(coef), ctypes.c_float(eps), _p(out), dtype_code(out.dtype), z.shape[0],
+                                     z.shape[1], out.shape[1], _stream()), "polynorm")
+    return out
+
+
+GATE_ALPHA = 1.702
+
+
+def gated_clamp(gate_up: torch.Tensor, ff: int, limit: float, out: torch.Tensor, scale_col: int = -1) -> torch.Tensor:
+    """out[t, f] = g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit), g and u columns f
+    and ff + f of the float rows of gate_up; with scale_col the row is also multiplied by sigmoid(gate_up[t, scale_col]).
+    out [rows, >= ff] (further columns zero)."""
+    _need(gate_up, torch.float32, "gate_up", 2); _need(out, None, "out", 2)
+    if gate_up.shape[1] < 2 * ff or out.shape[0] != gate_up.shape[0] or out.shape[1] < ff or scale_col >= gate_up.shape[1]:
+        raise KernelError("gated_clamp: shapes disagree")
+    _check(_ffn_rows().cisr_gated_clamp(_p(gate_up), gate_up.shape[1], ff, ctypes.c_float(limit), ctypes.c_float(GATE_ALPHA), scale_col,
+                                        _p(out), dtype_code(out.dtype), out.shape[0], out.shape[1], _stream()), "gated_clamp")
     return out
 
 
@@ -868,15 +1037,22 @@ def moe_jobs():
 
 
 def moe_select(logits: torch.Tensor, top: int, n_groups: int, keep: int, route_scale: float, chosen: torch.Tensor,
-               weight: torch.Tensor) -> None:
-    """Per token, from the router's logits (float [tokens, experts]): sigmoid scores, the open groups, the `top` chosen
-    experts (`chosen`, int32 [tokens, top], best first) and their weights score * route_scale (`weight`, float)."""
+               weight: torch.Tensor, scores: str = "sigmoid", choice_bias: Optional[torch.Tensor] = None) -> None:
+    """Per token, from the router's logits (float [tokens, experts]): scores (`scores`: "sigmoid" of each logit, or
+    "softmax" over all of them), the open groups, the `top` chosen experts (`chosen`, int32 [tokens, top], best first;
+    chosen by score + choice_bias where that is given) and their weights score * route_scale (`weight`, float)."""
     _need(logits, torch.float32, "logits", 2); _need(chosen, torch.int32, "chosen", 2); _need(weight, torch.float32, "weight", 2)
     tokens, experts = logits.shape
     if chosen.shape != (tokens, top) or weight.shape != (tokens, top):
         raise KernelError("moe_select: shapes disagree")
-    _check(_moe().cisr_moe_select(_p(logits), tokens, experts, top, n_groups, keep, ctypes.c_float(route_scale), _p(chosen),
-                                  _p(weight), _stream()), "moe_select")
+    if scores not in ("sigmoid", "softmax"):
+        raise KernelError(f"moe_select: unknown scores {scores!r}")
+    if choice_bias is not None:
+        _need(choice_bias, torch.float32, "choice_bias", 1)
+        if choice_bias.numel() != experts:
+            raise KernelError("moe_select: one choice bias per router output is needed")
+    _check(_moe().cisr_moe_select(_p(logits), tokens, experts, top, n_groups, keep, ctypes.c_float(route_scale),
+                                  int(scores == "softmax"), _p(choice_bias), _p(chosen), _p(weight), _stream()), "moe_select")
 
 
 def _channel_scale(scale: Optional[torch.Tensor], hidden: int, what: str) -> None:
@@ -887,21 +1063,26 @@ def _channel_scale(scale: Optional[torch.Tensor], hidden: int, what: str) -> Non
 
 
 def moe_rows(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
-             act: torch.Tensor, out: torch.Tensor, out_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+             act: torch.Tensor, out: torch.Tensor, out_scale: Optional[torch.Tensor] = None, gate_limit: Optional[float] = None) -> torch.Tensor:
     """out (float [tokens, hidden]) = sum over a token's chosen experts of weight * W_down_e relu(W_up_e h)^2, a warp per
     output feature; w_up [experts, ff, hidden], w_down [experts, hidden, ff]; `act` [tokens * top, ff] is scratch; `out_scale`
-    (float, one per channel) multiplies the sum."""
+    (float, one per channel) multiplies the sum.  With `gate_limit` the experts are gated: w_up [experts, 2 ff, hidden]
+    (gate rows, then up rows) and the activation is `gated_clamp`'s.  A chosen index beyond the experts that have
+    matrices is an identity expert: it adds weight * h."""
     _need(h, None, "h", 2); _need(w_up, h.dtype, "w_up", 3); _need(w_down, h.dtype, "w_down", 3); _need(act, h.dtype, "act", 2)
     _need(out, torch.float32, "out", 2); _need(chosen, torch.int32, "chosen", 2); _need(weight, torch.float32, "weight", 2)
     tokens, hidden = h.shape
     experts, ff, _ = w_up.shape
+    if gate_limit is not None:
+        ff //= 2
     top = chosen.shape[1]
     if (w_up.shape[2] != hidden or w_down.shape != (experts, hidden, ff) or act.shape != (tokens * top, ff)
             or out.shape != (tokens, hidden) or chosen.shape[0] != tokens or weight.shape != chosen.shape):
         raise KernelError("moe_rows: shapes disagree")
     _channel_scale(out_scale, hidden, "moe_rows")
     _check(_moe().cisr_moe_rows(_p(h), _p(w_up), _p(w_down), dtype_code(h.dtype), _p(chosen), _p(weight), tokens, hidden, ff, top,
-                                _p(act), _p(out_scale), _p(out), _stream()), "moe_rows", own=2)
+                                experts, int(gate_limit is not None), ctypes.c_float(gate_limit or 0.0), _p(act), _p(out_scale), _p(out),
+                                _stream()), "moe_rows", own=2)
     return out
 
 
@@ -909,10 +1090,12 @@ MOE_TILE = 128                   # rows per tile of the grouped product: each ex
 MOE_GROUPED_MIN_ROWS = 64        # (token, expert) pairs per expert, on average, from which sorting and the grouped product pay
 
 
-def moe_grouped_ok(h: torch.Tensor, w_up: torch.Tensor, top: int) -> bool:
+def moe_grouped_ok(h: torch.Tensor, w_up: torch.Tensor, top: int, gated: bool = False) -> bool:
     """Whether a step's experts run as grouped tcgen05 products: bfloat16, widths whose rows are 16-byte multiples, and
     enough pairs per expert that whole 128-row tiles are mostly real rows."""
     experts, ff, hidden = w_up.shape
+    if gated:
+        ff //= 2
     return (h.dtype == torch.bfloat16 and hidden % 8 == 0 and ff % 8 == 0 and h.shape[0] * top >= MOE_GROUPED_MIN_ROWS * experts
             and h.shape[0] >= TCGEN05_MIN_TOKENS)
 
@@ -947,27 +1130,33 @@ def moe_gather(h: torch.Tensor, src_token: torch.Tensor, sorted_h: torch.Tensor)
 
 
 def moe_combine(sorted_out: torch.Tensor, row_of: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
-                out_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t] = out_scale * sum over k of weight[t, k] * sorted_out[row_of[t * top + k]], in the order of k."""
+                out_scale: Optional[torch.Tensor] = None, h: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = out_scale * sum over k of weight[t, k] * sorted_out[row_of[t * top + k]], in the order of k; a pair
+    without a row (row_of < 0: an identity expert) adds weight[t, k] * h[t] (`h` bfloat16 [tokens, hidden])."""
+    if h is not None:
+        _need(h, torch.bfloat16, "h", 2)
     _need(sorted_out, torch.float32, "sorted_out", 2); _need(row_of, torch.int32, "row_of", 1); _need(weight, torch.float32, "weight", 2)
     _need(out, torch.float32, "out", 2)
     tokens, top = weight.shape
     if row_of.numel() != tokens * top or out.shape != (tokens, sorted_out.shape[1]):
         raise KernelError("moe_combine: shapes disagree")
     _channel_scale(out_scale, out.shape[1], "moe_combine")
-    _check(_moe().cisr_moe_combine(_p(sorted_out), _p(row_of), _p(weight), tokens, top, out.shape[1], _p(out_scale), _p(out), _stream()),
-           "moe_combine")
+    _check(_moe().cisr_moe_combine(_p(sorted_out), _p(row_of), _p(weight), tokens, top, out.shape[1], _p(h), _p(out_scale), _p(out),
+                                   _stream()), "moe_combine")
     return out
 
 
 def moe_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
-                out: torch.Tensor, out_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: torch.Tensor, out_scale: Optional[torch.Tensor] = None, gate_limit: Optional[float] = None) -> torch.Tensor:
     """The same sum as `moe_rows` for many tokens: pairs sorted by expert on the device, activations gathered into that
-    order, both products as grouped tcgen05 products (relu^2 as the first one's epilogue), rows summed per token with the
-    router's weights in the router's order.  Nothing is read back to the host."""
+    order, both products as grouped tcgen05 products (relu^2 as the first one's epilogue; gated experts: float sums of
+    the stacked gate and up rows, then `gated_clamp`), rows summed per token with the router's weights in the router's
+    order.  Nothing is read back to the host."""
     _need(w_up, torch.bfloat16, "w_up", 3); _need(w_down, torch.bfloat16, "w_down", 3)
     tokens, hidden = h.shape
     experts, ff, _ = w_up.shape
+    if gate_limit is not None:
+        ff //= 2
     top = chosen.shape[1]
     if w_up.shape[2] != hidden or w_down.shape != (experts, hidden, ff) or out.shape != (tokens, hidden) or weight.shape != chosen.shape:
         raise KernelError("moe_grouped: shapes disagree")
@@ -978,9 +1167,13 @@ def moe_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chose
     tile_group = torch.empty(rows // MOE_TILE, dtype=torch.int32, device=device)
     moe_sort(chosen, experts, row_of, src_token, tile_group)
     sorted_h = moe_gather(h, src_token, torch.empty((rows, hidden), dtype=torch.bfloat16, device=device))
-    act = gemm_tcgen05_grouped(sorted_h, w_up, torch.empty((rows, ff), dtype=torch.bfloat16, device=device), tile_group, tokens * top)
+    if gate_limit is None:
+        act = gemm_tcgen05_grouped(sorted_h, w_up, torch.empty((rows, ff), dtype=torch.bfloat16, device=device), tile_group, tokens * top)
+    else:
+        sums = gemm_tcgen05_grouped(sorted_h, w_up, torch.empty((rows, 2 * ff), dtype=torch.float32, device=device), tile_group, tokens * top)
+        act = gated_clamp(sums, ff, gate_limit, torch.empty((rows, ff), dtype=torch.bfloat16, device=device))
     sorted_out = gemm_tcgen05_grouped(act, w_down, torch.empty((rows, hidden), dtype=torch.float32, device=device), tile_group, tokens * top)
-    return moe_combine(sorted_out, row_of, weight, out, out_scale)
+    return moe_combine(sorted_out, row_of, weight, out, out_scale, h=h)
 
 
 # ------------------------------------------------------------------ sampling
@@ -1138,6 +1331,12 @@ def set_pdl(on: bool) -> None:
         _rows_state["lib"].cisr_attention_rows_set_pdl(int(on))
     if "lib" in _delta_state:
         _delta_state["lib"].cisr_delta_set_pdl(int(on))
+    if "lib" in _diff_state:
+        _diff_state["lib"].cisr_diff_set_pdl(int(on))
+    if "lib" in _depth_state:
+        _depth_state["lib"].cisr_depth_set_pdl(int(on))
+    if "lib" in _ffn_rows_state:
+        _ffn_rows_state["lib"].cisr_ffn_rows_set_pdl(int(on))
     if "lib" in _tcgen05_state:
         _tcgen05_state["lib"].cisr_gemm_tcgen05_set_pdl(int(on))
     for (source, _, _), lib in list(_attention_libs.items()):

@@ -194,19 +194,22 @@ def attention_step_plan(host):
 
 
 def paged_attention(plan, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cache, ctx, hq: int, hkv: int, scale: float,
-                    window, sink=None) -> torch.Tensor:
+                    window, sink=None, keep_first: int = 0) -> torch.Tensor:
     """Attention of a step's queries q [tokens, hq, D] over the pages of k and v ([pages, hkv, page, D]; the same tensor
     where a row serves as key and value), with the step's launch plan: the prompt kernel for portions, the split kernel
     and its merge for single tokens.  `sink`: a score whose exponential joins the softmax's denominator without a value
-    (None: ordinary softmax).  Returns [tokens, hq, D] in q's type."""
+    (None: ordinary softmax).  `keep_first`: the sequence's first keys that every later query keeps seeing behind the window.
+    Returns [tokens, hq, D] in q's type."""
     tokens, _, dim = q.shape
     out = torch.empty_like(q)
     if plan.info["n_tiles"] and kernels.attn_prefill_wide_ok(q, k, cache.page_size):
         kernels.attn_prefill_wide(q, out, k, v, ctx.req_slot, cache.block_table, plan["wide_req"], plan["wide_q0"],
-                                  ctx.q_start, ctx.q_len, ctx.ctx_len, hq, hkv, cache.page_size, scale, window, sink=sink)
+                                  ctx.q_start, ctx.q_len, ctx.ctx_len, hq, hkv, cache.page_size, scale, window, sink=sink,
+                                  keep_first=keep_first)
     elif plan.info["n_tiles"]:
         kernels.attn_prefill(q, out, k, v, ctx.req_slot, cache.block_table, plan["tile_req"], plan["tile_q0"],
-                             ctx.q_start, ctx.q_len, ctx.ctx_len, hq, hkv, cache.page_size, scale, window, sink=sink)
+                             ctx.q_start, ctx.q_len, ctx.ctx_len, hq, hkv, cache.page_size, scale, window, sink=sink,
+                             keep_first=keep_first)
     n_decode = plan.info["n_decode"]
     if n_decode:
         n_splits = plan.info["n_splits"]
@@ -214,5 +217,5 @@ def paged_attention(plan, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cac
         stats = torch.empty((n_decode, hq, n_splits, 2), dtype=torch.float32, device=q.device)
         kernels.attn_decode(q, out, k, v, ctx.req_slot, cache.block_table, plan["dec_req"], n_decode, ctx.q_start,
                             ctx.ctx_len, partial, stats, hq, hkv, cache.page_size, scale, window, DECODE_RANGE, n_splits,
-                            sink=sink)
+                            sink=sink, keep_first=keep_first)
     return out

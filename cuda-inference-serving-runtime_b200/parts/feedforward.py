@@ -124,3 +124,39 @@ class DenseMLP(FeedForward):
         act = torch.empty((tokens, self.down.shape[1]), dtype=self.dtype, device=h.device)
         kernels.activation(linear(h, self.up), act, self.activation)
         return linear(act, self.down)
+
+
+@register(FEED_FORWARDS, "polynorm_mlp")
+class PolyNormMLP(FeedForward):
+    """down(act(up(h))) without biases, act = a N(z) + b N(z^2) + c N(z^3) + e with powers taken element by element and
+    N(u) = u / sqrt(mean(u^2) + eps) over a token's ff values; (a, b, c, e) is a tensor of the layer.  params: hidden_size,
+    intermediate_size, eps; names (up, down, act).  The activation needs the whole row, so it is a row kernel between
+    the two products (float on the first product's float sums, rounded once)."""
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        self.eps = float(spec["eps"])
+        self.names = dict({"up": "up", "down": "down", "act": "act"}, **dict(spec.get("names", {})))
+        self.up = self.down = self.coef = None
+
+    def tensor_needs(self) -> Dict[str, TensorNeed]:
+        return {self.names["up"]: TensorNeed((self.inter, self.hidden)),
+                self.names["down"]: TensorNeed((self.hidden, self.inter)),
+                self.names["act"]: TensorNeed((4,), role="vector", init_mean=0.4, init_std=0.2)}
+
+    def load(self, tensors):
+        self.up = tensors[self.names["up"]].contiguous()
+        self.down = pad_columns(tensors[self.names["down"]], 8)
+        self.coef = tensors[self.names["act"]].float().contiguous()
+
+    def kernel_jobs(self):
+        return (kernels.ffn_rows_jobs() + kernels.gemm_jobs(self.dtype)
+                + (kernels.skinny_jobs() if self.dtype == torch.bfloat16 else []))
+
+    def forward(self, h, ctx):
+        h = as_tensor(h)
+        act = torch.empty((h.shape[0], self.down.shape[1]), dtype=self.dtype, device=h.device)
+        kernels.polynorm(linear(h, self.up), self.coef, self.eps, act)
+        return linear(act, self.down)

@@ -43,6 +43,19 @@ class RMSNorm(Norm):
                                    delta_scale=delta_scale)
 
 
+@register(NORMS, "rms_norm_scalar")
+class ScalarRMSNorm(RMSNorm):
+    """x / sqrt(mean(x^2) + eps) * g with ONE weight g for all channels (a tensor without dimensions).  params: size,
+    eps; weight_name.  The weight is spread over the channels at load, so every kernel that takes RMSNorm (the norm
+    kernel, the products' norm prologues, the kernels that end in a norm) takes this one as it is."""
+
+    def tensor_needs(self) -> Dict[str, TensorNeed]:
+        return {self.weight_name: TensorNeed((), role="vector")}
+
+    def load(self, tensors):
+        self.weight = tensors[self.weight_name].float().reshape(1).expand(self.size).contiguous()
+
+
 @register(NORMS, "layer_norm")
 class LayerNorm(Norm):
     """(x - mean) / sqrt(var + eps) * w over the channels, var the mean squared deviation, no bias.
