@@ -8,6 +8,7 @@ parts and the run list is data.
 from __future__ import annotations
 
 import json
+from dataclasses import replace
 from pathlib import Path
 from typing import Dict, List, Optional, Union
 
@@ -113,10 +114,18 @@ class Model:
 
     # ---------------------------------------------------------------- cache
     def cache_uses(self) -> list:
+        """Per run entry: what its mixer keeps, or the index of the entry whose pages it reads.  An entry whose pages
+        others read keeps what any of them still sees: the widest window (none, if a reader has none) and the most
+        kept first keys.  Each mixer masks by its own window whatever the pages hold."""
         uses = []
         for entry in self.spec.run:
             if entry.cache_of is not None:
                 uses.append(entry.cache_of)
+                owner, reader = uses[entry.cache_of], self.layers[entry.layer].mixer.cache_use()
+                if owner.kind == "pages" and reader.kind == "pages" and owner.window is not None:
+                    window = None if reader.window is None else max(owner.window, reader.window)
+                    keep = 0 if window is None else max(owner.keep_first, reader.keep_first)
+                    uses[entry.cache_of] = replace(owner, window=window, keep_first=keep)
             else:
                 uses.append(self.layers[entry.layer].mixer.cache_use())
         return uses

@@ -94,3 +94,17 @@ def test_a_state_besides_the_pages_is_the_entrys_own():
     assert float(own.state[1 - slot].sum()) == 20.0
     with pytest.raises(ValueError):
         CacheManager([pages], 4, 8, 2, 64, side_states=[pages])
+
+
+def test_pages_that_another_layer_reads_stay_while_either_mask_sees_them():
+    """A layer that reads another's keys and values masks them by its own window and kept first keys: the owner's pages
+    are kept by the wider of the two windows and the larger count of kept keys."""
+    uses = Model(spec_of(gm.GA), "float32", config=gm.GA, device=None).cache_uses()
+    assert uses[1] == 0 and uses[3] == 2
+    assert (uses[0].window, uses[0].keep_first) == (21, 18) and (uses[2].window, uses[2].keep_first) == (40, 1)
+    uses = Model(spec_of(gm.GC), "float32", config=gm.GC, device=None).cache_uses()
+    assert uses[0].window is None and uses[2] == 0
+    reader_without_window = copy.deepcopy(gm.GA)
+    reader_without_window["layers"][1]["mixer"].pop("mask")
+    uses = Model(spec_of(reader_without_window), "float32", config=reader_without_window, device=None).cache_uses()
+    assert uses[0].window is None and uses[0].keep_first == 0
