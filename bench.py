@@ -27,8 +27,9 @@ every request holding about 4096 tokens of context while it decodes.  Prints ONE
 --workload mixed: the continuous-batching workload (by default the SmolLM2-1.7B sizes, 64 requests with prompts
 of 128 to 2048 tokens, 256 generated tokens each) through the scheduler with graphs on; prints total, prefill
 and decode tokens per second, launch counts, graph statistics and a roofline for the whole run.
---designs SIZES [--design zurolorn|ronolorn]: Zurolorn (latent attention, routed experts) or Ronolorn (windowed attention,
-gated delta rule, several residual streams) beside the Llama shape of equal size at the named widths:
+--designs SIZES [--design zurolorn|ronolorn|gipozen]: Zurolorn (latent attention, routed experts), Ronolorn (windowed attention,
+gated delta rule, several residual streams) or Gipozen (differential attention with convolved projections, depth-weighted
+average of the stream, PolyNorm and routed gated feed-forwards) beside the Llama shape of equal size at the named widths:
 prompt and decode tokens per second of both, and per kind of kernel the device time and the distance from the roofline.
 --impl reference: the reference's own stock code on the same decode workload (see reference_arm).
 
@@ -465,6 +466,26 @@ def ronolorn_pair(width: int, layers: int, heads: int, ff_active: int, experts: 
     return rono, design_pair(width, layers, heads, ff_active, max(experts, 4), max(top, 1), vocab)[1]
 
 
+def gipozen_pair(width: int, layers: int, heads: int, ff_active: int, experts: int = 0, top: int = 0, vocab: int = 32000):
+    """A Gipozen shape and the Llama shape of equal size beside it: the same width, layers, vocabulary and query heads (two maps
+    of 32 per head fill the 64 numbers of a Llama head, values of 64) with a quarter as many key heads; windows of 1024 keys with 64
+    kept first ones, four taps.  Even layers own keys and values and have the dense PolyNorm feed-forward (two matrices, one and a
+    half times as wide as the gated one's three); odd layers read the layer before and have routed experts: `top` of `experts`
+    gated experts and a quarter as many identity outputs beside a shared expert, together as wide as the dense gated one."""
+    kv = max(1, heads // 4)
+    experts, top = max(experts, 4), max(top, 1)
+    mix = {"heads": heads, "kv_heads": kv, "dim": 32, "vdim": 64, "conv": 4, "scale": 32 ** -0.5, "diff": 0.6,
+           "mask": {"size": 1024, "keep_first": 64}}
+    dense = {"kind": "dense", "ff": ff_active * 3 // 2}
+    ff = ff_active // (top + 1) // 64 * 64
+    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "identity": max(1, experts // 4), "top": top},
+           "shared": {"ff": ff, "limit": 7.0}}
+    gipo = {"architecture": "Gipozen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0, "max_positions": 8192,
+            "layers": [{"type": "attention", "mixer": dict(mix, kv_from=i - 1) if i % 2 else mix, "mlp": moe if i % 2 else dense}
+                       for i in range(layers)]}
+    return gipo, design_pair(width, layers, heads, ff_active, experts, top, vocab)[1]
+
+
 DESIGN_SIZES = {"1024": (1024, 8, 16, 2048, 16, 4), "2048": (2048, 8, 32, 4096, 32, 4), "4096": (4096, 4, 32, 8192, 64, 8)}
 KERNEL_KIND = {   # which kernels of the two designs are alike
     "gemm_tcgen05": "product, many tokens", "gemm_library": "product, many tokens", "gemm_tcgen05_swiglu": "feed-forward product, many tokens",
@@ -475,7 +496,9 @@ KERNEL_KIND = {   # which kernels of the two designs are alike
     "latent_values": "product per head", "moe_select": "row kernels", "moe_gather": "row kernels",
     "moe_combine": "row kernels", "moe_sort": "bookkeeping", "stream_add": "row kernels", "swiglu": "row kernels",
     "hyper_mix_norm": "norm", "attention_rows": "row kernels", "activation": "row kernels", "delta_prepare": "row kernels",
-    "delta_output": "row kernels", "delta_keep": "bookkeeping", "delta_recurrence": "recurrence", "delta_chunks": "recurrence"}
+    "delta_output": "row kernels", "delta_keep": "bookkeeping", "delta_recurrence": "recurrence", "delta_chunks": "recurrence",
+    "diff_rows": "row kernels", "diff_combine": "row kernels", "conv_keep": "bookkeeping", "depth_mix_norm": "norm", "polynorm": "row kernels",
+    "gated_clamp": "row kernels"}
 
 
 def generic_need(name: str, shape: tuple, cache_tokens: int, causal: int):
@@ -536,6 +559,22 @@ def generic_need(name: str, shape: tuple, cache_tokens: int, causal: int):
         # (seven operations per state element and token), which the tensor-core peak does not describe: bytes only
         tokens, n_req, heads, kvh, dk, dv = shape
         return (n_req * 2 * heads * dk * dv + tokens * (2 * kvh * dk + 2 * heads * dv + 2 * heads)) * 4, 0.0
+    if name == "diff_rows":
+        tokens, channels, taps, q_cols, kv_cols = shape
+        return tokens * (channels * 4 + (q_cols + 2 * kv_cols) * 2), 2.0 * tokens * channels * taps
+    if name == "conv_keep":
+        n_req, channels, taps = shape
+        return n_req * (taps - 1) * channels * 8, 0.0
+    if name == "diff_combine":
+        tokens, out_cols, mixed_cols = shape
+        return tokens * (mixed_cols * 2 + out_cols * 6), 0.0
+    if name == "depth_mix_norm":
+        rows, n_new, hidden, added, stored, normed = shape
+        return rows * hidden * (4 * (n_new + 1 + (1 if added else 0) + (2 if stored else 0)) + (2 if normed else 0)), 0.0
+    if name == "polynorm":
+        return shape[0] * shape[1] * 6, 0.0
+    if name == "gated_clamp":
+        return shape[0] * shape[1] * 10, 0.0
     if name == "add_rmsnorm":
         rows, hidden, added = shape
         return rows * hidden * (4 + (8 if added else 0) + 2), 0.0
@@ -613,7 +652,7 @@ def design_comparison(args, hbm_gbs: float, burst_tflops: float, peak_source: st
 
     sizes = [s for s in args.designs.split(",") if s]
     batch, context, prompt = args.batch, min(args.context, 2048), PREFILL_TOKENS
-    pair = ronolorn_pair if args.design == "ronolorn" else design_pair
+    pair = {"ronolorn": ronolorn_pair, "gipozen": gipozen_pair}.get(args.design, design_pair)
     line = {"designs": f"{args.design} beside llama at equal size", "dtype": "bf16", "data": "synthetic token ids, seeded random weights",
             "batch": batch, "context": context, "prompt_tokens": prompt, "peaks": peak_source, "sizes": {}}
     sampler = ClockSampler().start()
@@ -876,9 +915,10 @@ def main() -> int:
     parser.add_argument("--designs", metavar="SIZES", default=None,
                         help="instead of the default workload: Zurolorn beside the Llama shape of equal size, prompt and decode, at "
                              "the named widths (comma-separated, from 1024, 2048, 4096)")
-    parser.add_argument("--design", choices=["zurolorn", "ronolorn"], default="zurolorn",
+    parser.add_argument("--design", choices=["zurolorn", "ronolorn", "gipozen"], default="zurolorn",
                         help="--designs: which design stands beside the Llama shape (ronolorn: windowed attention, gated delta rule, "
-                             "four residual streams, dense feed-forward)")
+                             "four residual streams, dense feed-forward; gipozen: differential attention, depth-weighted average, "
+                             "PolyNorm and routed gated feed-forwards)")
     args = parser.parse_args()
     if args.workload == "mixed" and "--preset" not in " ".join(sys.argv):
         args.preset = "smollm2-1.7b"

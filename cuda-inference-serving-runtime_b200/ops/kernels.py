@@ -1635,7 +1635,7 @@ _DESCRIBE = {
     "moe_rows": lambda h, w_up, w_down, chosen, *a, **kw: (int(h.shape[0]), int(w_up.shape[0]), int(w_up.shape[1]), int(w_up.shape[2]), int(chosen.shape[1])),
     "moe_sort": lambda chosen, experts, *a: (int(chosen.shape[0]), int(chosen.shape[1]), int(experts)),
     "moe_gather": lambda h, src_token, sorted_h: (int(sorted_h.shape[0]), int(sorted_h.shape[1])),
-    "moe_combine": lambda sorted_out, row_of, weight, out, out_scale=None: (int(out.shape[0]), int(weight.shape[1]), int(out.shape[1])),
+    "moe_combine": lambda sorted_out, row_of, weight, out, out_scale=None, h=None: (int(out.shape[0]), int(weight.shape[1]), int(out.shape[1])),
     "gemm_tcgen05_grouped": lambda a, w, out, tile_group, rows_in_use=None:
         (int(rows_in_use or a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2]), out.dtype == torch.bfloat16),
     "gemm_heads": lambda a, w, out, w_is_nk: (int(a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2])),
@@ -1655,6 +1655,15 @@ _DESCRIBE = {
     "delta_recurrence": lambda qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim, lanes=0, below=0:
         (int(qkv.shape[0]), int(n_req), int(heads), int(kv_heads), int(key_dim), int(value_dim)),
     "delta_output": lambda o, proj, *a: (int(o.shape[0]), int(o.shape[1] * o.shape[2])),
+    "diff_rows": lambda proj, conv_w, taps, state, **kw: (int(proj.shape[0]), int(conv_w.shape[0]), int(taps), int(kw["q_out"].shape[1] * kw["q_out"].shape[2]),
+                                                         0 if kw.get("k_cache") is None else int(kw["k_cache"].shape[1] * kw["k_cache"].shape[3])),
+    "conv_keep": lambda proj, state, req_slot, q_start, q_len, n_req, taps, channels: (int(n_req), int(channels), int(taps)),
+    "diff_combine": lambda mixed, gate, gate_col, out, *a: (int(out.shape[0]), int(out.shape[1]), int(mixed.shape[1] * mixed.shape[2])),
+    "depth_mix_norm": lambda hist, x, pending, w, n_new, **kw:
+        (int(x.shape[0] if kw.get("rows") is None else kw["rows"].numel()), int(n_new), int(x.shape[1]), pending is not None,
+         bool(kw.get("store", True)) and kw.get("rows") is None, kw.get("h") is not None),
+    "polynorm": lambda z, coef, eps, out: (int(z.shape[0]), int(z.shape[1])),
+    "gated_clamp": lambda gate_up, ff, limit, out, scale_col=-1: (int(out.shape[0]), int(ff)),
     "rope_store": lambda proj, *rest, **kw: (int(proj.shape[0]), int(proj.shape[1])),
     "page_copy": lambda *a, **kw: (),
     "table_update": lambda *a, **kw: (),
