@@ -489,7 +489,8 @@ def gipozen_pair(width: int, layers: int, heads: int, ff_active: int, experts: i
 DESIGN_SIZES = {"1024": (1024, 8, 16, 2048, 16, 4), "2048": (2048, 8, 32, 4096, 32, 4), "4096": (4096, 4, 32, 8192, 64, 8)}
 KERNEL_KIND = {   # which kernels of the two designs are alike
     "gemm_tcgen05": "product, many tokens", "gemm_library": "product, many tokens", "gemm_tcgen05_swiglu": "feed-forward product, many tokens",
-    "gemm_tcgen05_rope": "product, many tokens", "gemm_tcgen05_grouped": "feed-forward product, many tokens", "skinny_gemm": "product, few tokens",
+    "gemm_tcgen05_rope": "product, many tokens", "gemm_tcgen05_grouped": "feed-forward product, many tokens",
+    "gemm_tcgen05_grouped_gated": "feed-forward product, many tokens", "skinny_gemm": "product, few tokens",
     "moe_rows": "feed-forward product, few tokens", "gemm_heads": "product per head", "attn_prefill_wide": "prompt attention", "attn_prefill": "prompt attention",
     "attn_decode": "decode attention", "merge_out_proj": "product, few tokens", "add_rmsnorm": "norm", "embedding": "row kernels", "rope_store": "row kernels",
     "latent_rows": "row kernels", "latent_query": "row kernels", "latent_gate": "row kernels", "latent_absorb": "product per head",
@@ -512,6 +513,9 @@ def generic_need(name: str, shape: tuple, cache_tokens: int, causal: int):
     if name == "gemm_tcgen05_grouped":
         m, groups, n, k, relu2 = shape
         return (m * k + groups * n * k) * 2 + m * n * (2 if relu2 else 4), 2.0 * m * n * k
+    if name == "gemm_tcgen05_grouped_gated":
+        m, groups, n2, k = shape
+        return (m * k + groups * n2 * k) * 2 + m * (n2 // 2) * 2, 2.0 * m * n2 * k
     if name == "gemm_heads":
         m, heads, a, b = shape
         return heads * a * b * 2 + m * heads * (a + b) * 2, 2.0 * m * heads * a * b

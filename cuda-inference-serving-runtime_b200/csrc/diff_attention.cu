@@ -20,20 +20,29 @@ static bool g_pdl = false;
 CISR_EXPORT void cisr_diff_set_pdl(int on) { g_pdl = on != 0; }
 
 namespace {
-// y_t[c] = sum_j w[c][j] * u_(t - taps + 1 + j)[c]; `local` is the token's index inside its portion.
+// y_t[c] = sum_j w[j][c] * u_(t - taps + 1 + j)[c], w stored tap by tap [taps][channels] so that a warp's lanes read
+// neighbouring weights; `local` is the token's index inside its portion.
 __device__ __forceinline__ float conv_at(const float* __restrict__ proj, int row_stride, const float* __restrict__ conv_w,
                                          const float* __restrict__ keep, int channels, int taps, int t, int local, int c) {
     float acc = 0.f;
     for (int j = taps - 1; j >= 0; --j) {                 // oldest input first
         const int at = local - j;
         const float x = at >= 0 ? proj[(size_t)(t - j) * row_stride + c] : keep[(size_t)(taps - 1 + at) * channels + c];
-        acc = fmaf(conv_w[(size_t)c * taps + (taps - 1 - j)], x, acc);
+        acc = fmaf(conv_w[(size_t)(taps - 1 - j) * channels + c], x, acc);
     }
     return acc;
 }
 
+template <typename T> __device__ __forceinline__ void store_pair(T* dst, float a, float b);
+template <> __device__ __forceinline__ void store_pair<float>(float* dst, float a, float b) { *reinterpret_cast<float2*>(dst) = make_float2(a, b); }
+template <> __device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloat16* dst, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(a, b);
+}
+
 // proj [tokens, row_stride] float; its first `channels` columns are the convolved ones: [q: hq * 2 * dk] and, when
 // write_kv, [k: hkv * 2 * dk][v: hkv * dv].  keep: the request's row of the state tensor, [taps - 1][channels].
+// A warp per row of `width` numbers (2 * hq query rows, then hkv key rows with their value rows), two neighbouring
+// numbers per lane; blockIdx.y shares a token's rows among CTAs where a step has few tokens.  width is even.
 template <typename T>
 __global__ void __launch_bounds__(256)
 diff_rows_kernel(const float* __restrict__ proj, int row_stride, const float* __restrict__ conv_w, int taps,
@@ -50,27 +59,40 @@ diff_rows_kernel(const float* __restrict__ proj, int row_stride, const float* __
     const float* keep = state + (size_t)slot * state_stride;
     const int nq = hq * 2 * dk, nk = hkv * 2 * dk;
     const int channels = nq + (write_kv ? nk + hkv * dv : 0);
+    const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     pdl_wait();
-    // query rows: head pair (h, m) is row 2 h + m, its numbers at columns [m * dk, (m + 1) * dk)
+    int page = -1;                                         // a padding row of a fixed-size batch: its slot holds no pages
+    if (write_kv) page = block_table[(size_t)slot * table_width + pos / page_size];
+    const int rows = 2 * hq + (page >= 0 ? hkv : 0);
     T* q_row = q_out + (size_t)t * 2 * hq * width;
-    for (int e = threadIdx.x; e < 2 * hq * width; e += blockDim.x) {
-        const int row = e / width, d = e - row * width, m = row & 1;
-        const int i = d - m * dk;
-        float v = 0.f;
-        if (i >= 0 && i < dk) v = conv_at(proj, row_stride, conv_w, keep, channels, taps, t, local, row * dk + i);
-        q_row[e] = from_float<T>(v);
-    }
-    if (!write_kv) return;
-    const int page = block_table[(size_t)slot * table_width + pos / page_size];
-    if (page < 0) return;                                 // a padding row of a fixed-size batch: its slot holds no pages
-    const size_t at = ((size_t)page * hkv * page_size + pos % page_size) * width;      // + g * page_size * width
-    for (int e = threadIdx.x; e < hkv * width; e += blockDim.x) {
-        const int g = e / width, d = e - g * width;
-        const float kv = d < 2 * dk ? conv_at(proj, row_stride, conv_w, keep, channels, taps, t, local, nq + g * 2 * dk + d) : 0.f;
-        const float vv = d < dv ? conv_at(proj, row_stride, conv_w, keep, channels, taps, t, local, nq + nk + g * dv + d) : 0.f;
-        const size_t dst = at + (size_t)g * page_size * width + d;
-        k_cache[dst] = from_float<T>(kv);
-        v_cache[dst] = from_float<T>(vv);
+    for (int row = blockIdx.y * warps + (threadIdx.x >> 5); row < rows; row += gridDim.y * warps) {
+        if (row < 2 * hq) {
+            // query rows: head pair (h, m) is row 2 h + m, its numbers at columns [m * dk, (m + 1) * dk)
+            const int first = (row & 1) * dk;
+            for (int d = 2 * lane; d < width; d += 64) {
+                float y[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int at = d + i - first;
+                    y[i] = at >= 0 && at < dk ? conv_at(proj, row_stride, conv_w, keep, channels, taps, t, local, row * dk + at) : 0.f;
+                }
+                store_pair<T>(q_row + (size_t)row * width + d, y[0], y[1]);
+            }
+        } else {
+            const int g = row - 2 * hq;
+            const size_t dst = ((size_t)page * hkv * page_size + (size_t)g * page_size + pos % page_size) * width;
+            for (int d = 2 * lane; d < width; d += 64) {
+                float kk[2], vv[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int e = d + i;
+                    kk[i] = e < 2 * dk ? conv_at(proj, row_stride, conv_w, keep, channels, taps, t, local, nq + g * 2 * dk + e) : 0.f;
+                    vv[i] = e < dv ? conv_at(proj, row_stride, conv_w, keep, channels, taps, t, local, nq + nk + g * dv + e) : 0.f;
+                }
+                store_pair<T>(k_cache + dst + d, kk[0], kk[1]);
+                store_pair<T>(v_cache + dst + d, vv[0], vv[1]);
+            }
+        }
     }
 }
 
@@ -128,13 +150,18 @@ CISR_EXPORT int cisr_diff_rows(const float* proj, int row_stride, const float* c
                                int table_width, int page_size, int tokens, int hq, int hkv, int dk, int dv, int width, int write_kv,
                                void* stream) {
     if (tokens <= 0) return 0;
-    if (taps < 1 || width < 2 * dk || width < dv || hq <= 0 || hkv <= 0) return -2;
+    if (taps < 1 || width < 2 * dk || width < dv || width % 2 || hq <= 0 || hkv <= 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
+    // eight rows per CTA; as many CTAs per token as bring a small step to about two per SM
+    const int rows = 2 * hq + (write_kv ? hkv : 0);
+    int share = (rows + 7) / 8, want = (296 + tokens - 1) / tokens;
+    share = share < want ? share : want;
+    const dim3 grid(tokens, share < 1 ? 1 : share);
     if (dtype == CISR_BF16)
-        return launch_kernel(diff_rows_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, s, g_pdl, proj, row_stride, conv_w, taps, state,
+        return launch_kernel(diff_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, g_pdl, proj, row_stride, conv_w, taps, state,
                              state_stride, token_req, req_slot, q_start, positions, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
                              (__nv_bfloat16*)v_cache, block_table, table_width, page_size, hq, hkv, dk, dv, width, write_kv);
-    return launch_kernel(diff_rows_kernel<float>, dim3(tokens), dim3(256), 0, s, g_pdl, proj, row_stride, conv_w, taps, state, state_stride,
+    return launch_kernel(diff_rows_kernel<float>, grid, dim3(256), 0, s, g_pdl, proj, row_stride, conv_w, taps, state, state_stride,
                          token_req, req_slot, q_start, positions, (float*)q_out, (float*)k_cache, (float*)v_cache, block_table,
                          table_width, page_size, hq, hkv, dk, dv, width, write_kv);
 }

@@ -27,11 +27,14 @@
 
 namespace {
 typedef __nv_bfloat16 bf16;
-enum : int { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ROPE = 2, EPI_RELU2 = 3 };
+enum : int { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ROPE = 2, EPI_RELU2 = 3, EPI_GATED = 4 };
+// SWIGLU and GATED: the B tile is BN / 2 gate rows and the BN / 2 up rows of the same features
+__host__ __device__ constexpr bool paired_rows(int epi) { return epi == EPI_SWIGLU || epi == EPI_GATED; }
 constexpr int BK = 64, UMMA_K = 16;     // BM = 128 (tcgen05.cuh)
 
 struct Epilogue {                       // what the epilogue variants need beyond the accumulator
     float* out_f32; bf16* out_bf16; int inter;
+    float limit, alpha;                 // GATED: g' = min(g, limit), u' = clamp(u, +-limit), g' sigmoid(alpha g') (u' + 1)
     int accumulate;                     // PLAIN: out += product (the residual stream, in place) instead of out = product
     const float* cos_t; const float* sin_t; bf16* q_out; bf16* k_cache; bf16* v_cache; const int* positions;
     const int* token_req; const int* req_slot; const int* block_table; int table_width; int page_size; int hq; int hkv; int dim;
@@ -115,6 +118,23 @@ __device__ __forceinline__ void epilogue_tile(const Epilogue& ep, uint32_t lane_
 #pragma unroll
             for (int j = 0; j < 32; ++j) { const float r = fmaxf(__uint_as_float(v[j]), 0.f); act[j] = r * r; }
             if (row < m && n0 + c < n) store_bf16x32(ep.out_bf16 + (size_t)row * n + n0 + c, act, n - (n0 + c));
+        }
+    } else if (EPI == EPI_GATED) {
+        // the clamped gated activation of an expert's stacked gate and up rows, as bfloat16 [m, inter]
+        const float limit = ep.limit, alpha = ep.alpha;
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+            uint32_t g[32], u[32];
+            tmem_load32(lane_base + (uint32_t)c, g);
+            tmem_load32(lane_base + (uint32_t)(BN / 2 + c), u);
+            float act[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float gv = fminf(__uint_as_float(g[j]), limit), uv = fminf(fmaxf(__uint_as_float(u[j]), -limit), limit);
+                act[j] = gv / (1.f + expf(-alpha * gv)) * (uv + 1.f);
+            }
+            if (row < m && n0 + c < ep.inter)
+                store_bf16x32(ep.out_bf16 + (size_t)row * ep.inter + n0 + c, act, ep.inter - (n0 + c));
         }
     } else if (EPI == EPI_SWIGLU) {
 #pragma unroll 1
@@ -200,7 +220,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = (k + BK - 1) / BK;
     const int total_tiles = tiles_m * tiles_n;
-    constexpr int TILE_N = EPI == EPI_SWIGLU ? BN / 2 : BN;   // SWIGLU: 128 accumulator columns are 64 gate + 64 up features
+    constexpr int TILE_N = paired_rows(EPI) ? BN / 2 : BN;    // paired: 128 accumulator columns are 64 gate + 64 up features
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
@@ -222,7 +242,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             auto load_b = [&](int s, int kb, int n0) {
                 unsigned char* b_tile = tiles + s * (S::A_BYTES + S::B_BYTES) + S::A_BYTES;
-                if (EPI == EPI_SWIGLU) {      // two boxes of BN/2 rows: gate rows n0.., up rows inter + n0..
+                if (paired_rows(EPI)) {       // two boxes of BN/2 rows: gate rows n0.., up rows inter + n0..
                     tma_load_2d(b_tile, &map_w, kb * BK, n0, full_bar + s);
                     tma_load_2d(b_tile + S::B_BYTES / 2, &map_w, kb * BK, ep.inter + n0, full_bar + s);
                 } else {
@@ -335,7 +355,7 @@ int launch(const void* a, const void* w, const Epilogue& ep, int m, int n, int k
     CUtensorMap map_a, map_w;
     int status = cached_map(&map_a, a, m, k, BM);
     if (status) return status;
-    if ((status = cached_map(&map_w, w, (long long)groups * n, k, EPI == EPI_SWIGLU ? BN / 2 : BN))) return status;
+    if ((status = cached_map(&map_w, w, (long long)groups * n, k, paired_rows(EPI) ? BN / 2 : BN))) return status;
     typedef Smem<BN, STAGES> S;
     static bool configured = false;
     if (!configured) {
@@ -480,4 +500,24 @@ CISR_EXPORT int cisr_gemm_tcgen05_grouped(const void* a, const void* w, void* ou
     ep.out_f32 = (float*)out;
     if (wide) return launch<256, 4, EPI_PLAIN>(a, w, ep, m, n, k, (n + 255) / 256, s, groups);
     return launch<128, 3, EPI_PLAIN>(a, w, ep, m, n, k, (n + 127) / 128, s, groups);
+}
+
+// The grouped product of gated experts with the activation as its epilogue: w [groups * 2 * inter, k] holds, per group,
+// inter gate rows and then inter up rows; out is bfloat16 [m, inter] = g' sigmoid(alpha g') (u' + 1) with
+// g' = min(gate, limit), u' = clamp(up, -limit, limit).  Rows and tile_group as for the grouped product above.
+CISR_EXPORT int cisr_gemm_tcgen05_grouped_gated(const void* a, const void* w, void* out, int m, int inter, int k, int groups,
+                                                const int* tile_group, float limit, float alpha, void* stream) {
+    if (m <= 0 || inter <= 0) return 0;
+    if (!g_encode || !g_error) return -13;
+    if (!operands_ok(a, w, k) || ((uintptr_t)out & 15) || m % BM || !tile_group || groups <= 0) return -2;
+    Epilogue ep = {};
+    ep.tile_group = tile_group;
+    ep.out_bf16 = (bf16*)out;
+    ep.inter = inter;
+    ep.limit = limit;
+    ep.alpha = alpha;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (wide_tiles(m, (inter + 127) / 128))
+        return launch<256, 4, EPI_GATED>(a, w, ep, m, 2 * inter, k, (inter + 127) / 128, s, groups);
+    return launch<128, 3, EPI_GATED>(a, w, ep, m, 2 * inter, k, (inter + 63) / 64, s, groups);
 }

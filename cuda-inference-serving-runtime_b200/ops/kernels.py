@@ -575,8 +575,8 @@ def diff_jobs():
 def diff_rows(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, state: torch.Tensor, *, token_req, req_slot, q_start, positions,
               q_out: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], block_table, page_size: int,
               hq: int, hkv: int, key_dim: int, value_dim: int) -> None:
-    """Per token of a step: the causal convolution over time (taps weights per channel, conv_w float [channels, taps], the
-    last one the current token's; inputs before the portion from `state` [slots, taps - 1, channels], zeros before the
+    """Per token of a step: the causal convolution over time (taps weights per channel, tap by tap: conv_w float [taps,
+    channels], the last row the current token's; inputs before the portion from `state` [slots, taps - 1, channels], zeros before the
     sequence) of the first columns of proj (float [tokens, cols]: q [hq * 2 * key_dim], then, when caches are given, k
     [hkv * 2 * key_dim] and v [hkv * value_dim]); the two maps of head h become query rows 2 h and 2 h + 1 of q_out
     [tokens, 2 hq, D] (map m at columns [m * key_dim, (m + 1) * key_dim), zeros elsewhere), a key row [k1 | k2 | 0] and a
@@ -586,7 +586,7 @@ def diff_rows(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, state: torch.
     tokens, width = q_out.shape[0], q_out.shape[2]
     write = k_cache is not None
     channels = hq * 2 * key_dim + ((hkv * 2 * key_dim + hkv * value_dim) if write else 0)
-    if (proj.shape[0] != tokens or proj.shape[1] < channels or tuple(conv_w.shape) != (channels, taps) or q_out.shape[1] != 2 * hq
+    if (proj.shape[0] != tokens or proj.shape[1] < channels or tuple(conv_w.shape) != (taps, channels) or q_out.shape[1] != 2 * hq
             or state[0].numel() != max(taps - 1, 0) * channels and taps > 1):
         raise KernelError("diff_rows: shapes disagree")
     if write:
@@ -1149,8 +1149,8 @@ def moe_combine(sorted_out: torch.Tensor, row_of: torch.Tensor, weight: torch.Te
 def moe_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
                 out: torch.Tensor, out_scale: Optional[torch.Tensor] = None, gate_limit: Optional[float] = None) -> torch.Tensor:
     """The same sum as `moe_rows` for many tokens: pairs sorted by expert on the device, activations gathered into that
-    order, both products as grouped tcgen05 products (relu^2 as the first one's epilogue; gated experts: float sums of
-    the stacked gate and up rows, then `gated_clamp`), rows summed per token with the router's weights in the router's
+    order, both products as grouped tcgen05 products (the activation, relu^2 or the clamped gated form over the stacked
+    gate and up rows, as the first one's epilogue), rows summed per token with the router's weights in the router's
     order.  Nothing is read back to the host."""
     _need(w_up, torch.bfloat16, "w_up", 3); _need(w_down, torch.bfloat16, "w_down", 3)
     tokens, hidden = h.shape
@@ -1170,8 +1170,8 @@ def moe_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chose
     if gate_limit is None:
         act = gemm_tcgen05_grouped(sorted_h, w_up, torch.empty((rows, ff), dtype=torch.bfloat16, device=device), tile_group, tokens * top)
     else:
-        sums = gemm_tcgen05_grouped(sorted_h, w_up, torch.empty((rows, 2 * ff), dtype=torch.float32, device=device), tile_group, tokens * top)
-        act = gated_clamp(sums, ff, gate_limit, torch.empty((rows, ff), dtype=torch.bfloat16, device=device))
+        act = gemm_tcgen05_grouped_gated(sorted_h, w_up, torch.empty((rows, ff), dtype=torch.bfloat16, device=device), tile_group,
+                                         gate_limit, tokens * top)
     sorted_out = gemm_tcgen05_grouped(act, w_down, torch.empty((rows, hidden), dtype=torch.float32, device=device), tile_group, tokens * top)
     return moe_combine(sorted_out, row_of, weight, out, out_scale, h=h)
 
@@ -1474,6 +1474,7 @@ def _tcgen05():
         lib.cisr_gemm_tcgen05_swiglu.restype = ctypes.c_int
         lib.cisr_gemm_tcgen05_rope.restype = ctypes.c_int
         lib.cisr_gemm_tcgen05_grouped.restype = ctypes.c_int
+        lib.cisr_gemm_tcgen05_grouped_gated.restype = ctypes.c_int
         _check(lib.cisr_gemm_tcgen05_init(_p(_error_flag())), "tcgen05 gemm init", own=0)
         lib.cisr_gemm_tcgen05_set_pdl(int(_pdl_state["on"]))
         _tcgen05_state["lib"] = lib
@@ -1536,6 +1537,22 @@ def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ti
 def tcgen05_rope_ok(dim: int, rot_half: int, interleaved: bool) -> bool:
     """The rotation epilogue takes heads of 64 or 128 rotated over their whole width in split-half pairs."""
     return dim in (64, 128) and 2 * rot_half == dim and not interleaved
+
+
+def gemm_tcgen05_grouped_gated(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor, limit: float,
+                               rows_in_use: Optional[int] = None) -> torch.Tensor:
+    """The grouped product of gated experts with the activation as its epilogue: rows of `a` as for `gemm_tcgen05_grouped`,
+    w bfloat16 [groups, 2 ff, K] (a group's gate rows, then its up rows), out bfloat16 [M, ff] =
+    g' sigmoid(1.702 g') (u' + 1) with g' = min(gate, limit), u' = clamp(up, -limit, limit) from the float sums."""
+    _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 3); _need(out, torch.bfloat16, "out", 2); _need(tile_group, torch.int32, "tile_group", 1)
+    m, k = a.shape
+    groups, n2, _ = w.shape
+    ff = out.shape[1]
+    if w.shape[2] != k or n2 != 2 * ff or out.shape[0] != m or m % 128 or tile_group.numel() != m // 128:
+        raise KernelError(f"gemm grouped gated: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
+    _check(_tcgen05().cisr_gemm_tcgen05_grouped_gated(_p(a), _p(w), _p(out), m, ff, k, groups, _p(tile_group), ctypes.c_float(limit),
+                                                      ctypes.c_float(GATE_ALPHA), _stream()), "gemm_tcgen05_grouped_gated")
+    return out
 
 
 def gemm_tcgen05_rope(a: torch.Tensor, w: torch.Tensor, rope: dict) -> None:
@@ -1638,6 +1655,8 @@ _DESCRIBE = {
     "moe_combine": lambda sorted_out, row_of, weight, out, out_scale=None, h=None: (int(out.shape[0]), int(weight.shape[1]), int(out.shape[1])),
     "gemm_tcgen05_grouped": lambda a, w, out, tile_group, rows_in_use=None:
         (int(rows_in_use or a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2]), out.dtype == torch.bfloat16),
+    "gemm_tcgen05_grouped_gated": lambda a, w, out, tile_group, limit, rows_in_use=None:
+        (int(rows_in_use or a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2])),
     "gemm_heads": lambda a, w, out, w_is_nk: (int(a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2])),
     "swiglu": lambda gate_up, out: (int(out.shape[0]), int(out.shape[1])),
     "rotary_tables": lambda positions, inv_freq, cos, sin, magnitude=1.0: (int(cos.shape[0]), int(cos.shape[1])),
@@ -1655,7 +1674,7 @@ _DESCRIBE = {
     "delta_recurrence": lambda qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim, lanes=0, below=0:
         (int(qkv.shape[0]), int(n_req), int(heads), int(kv_heads), int(key_dim), int(value_dim)),
     "delta_output": lambda o, proj, *a: (int(o.shape[0]), int(o.shape[1] * o.shape[2])),
-    "diff_rows": lambda proj, conv_w, taps, state, **kw: (int(proj.shape[0]), int(conv_w.shape[0]), int(taps), int(kw["q_out"].shape[1] * kw["q_out"].shape[2]),
+    "diff_rows": lambda proj, conv_w, taps, state, **kw: (int(proj.shape[0]), int(conv_w.shape[1]), int(taps), int(kw["q_out"].shape[1] * kw["q_out"].shape[2]),
                                                          0 if kw.get("k_cache") is None else int(kw["k_cache"].shape[1] * kw["k_cache"].shape[3])),
     "conv_keep": lambda proj, state, req_slot, q_start, q_len, n_req, taps, channels: (int(n_req), int(channels), int(taps)),
     "diff_combine": lambda mixed, gate, gate_col, out, *a: (int(out.shape[0]), int(out.shape[1]), int(mixed.shape[1] * mixed.shape[2])),

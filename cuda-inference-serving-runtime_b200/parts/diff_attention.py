@@ -85,7 +85,8 @@ class DiffAttention(Mixer):
         n = self.names
         which = ("q",) if self.shared_kv else ("q", "k", "v")
         self.w_in = torch.cat([tensors[n[w]] for w in which] + [tensors[n["gate"]]], dim=0).contiguous()     # convolved columns first
-        self.conv_w = torch.cat([tensors[n[w + "_conv"]].float() for w in which], dim=0).contiguous()
+        # tap by tap [taps, channels]: neighbouring channels are neighbours in memory, as the row kernel's lanes read them
+        self.conv_w = torch.cat([tensors[n[w + "_conv"]].float() for w in which], dim=0).t().contiguous()
         self.o = tensors[n["o"]].contiguous()
         l = {name: tensors[n[name]].float() for name in ("lq1", "lk1", "lq2", "lk2")}
         # one number for the layer, in float: exp(lq1 . lk1) - exp(lq2 . lk2) + diff

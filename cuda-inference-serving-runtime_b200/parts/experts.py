@@ -23,7 +23,7 @@ import torch
 
 from ..ops import kernels
 from .base import FEED_FORWARDS, FeedForward, TensorNeed, register
-from .linear import linear
+from .linear import linear, linear_add
 
 ACTIVATIONS = ("relu_squared", "gated_clamp")
 DEFAULT_NAMES = {"router": "router.weight", "up": "experts.{}.up.weight", "down": "experts.{}.down.weight",
@@ -123,13 +123,13 @@ class RoutedExperts(FeedForward):
                            choice_bias=self.choice_bias)
         return chosen, weight
 
-    def shared_expert(self, h: torch.Tensor) -> torch.Tensor:
-        """sigmoid(w_sg . h) * W_down act(W_gate h, W_up h): the factor is applied to the activations (the product after it
-        is linear), in float, before their one rounding."""
+    def shared_expert(self, h: torch.Tensor, into: torch.Tensor) -> torch.Tensor:
+        """into += sigmoid(w_sg . h) * W_down act(W_gate h, W_up h): the factor is applied to the activations (the product
+        after it is linear), in float, before their one rounding; the add is the last product's epilogue."""
         sums = linear(h, self.shared_in)                   # float [tokens, gate | up | factor logit]
         act = torch.empty((h.shape[0], self.shared_down.shape[1]), dtype=self.dtype, device=h.device)
         kernels.gated_clamp(sums, self.shared_size, self.shared_limit, act, scale_col=2 * self.shared_size)
-        return linear(act, self.shared_down)
+        return linear_add(act, self.shared_down, into)
 
     def forward(self, h, ctx, out_scale=None):
         tokens = h.shape[0]
@@ -143,5 +143,5 @@ class RoutedExperts(FeedForward):
             act = torch.empty((tokens * self.top, self.ff), dtype=self.dtype, device=h.device)
             kernels.moe_rows(h, self.up, self.down, chosen, weight, act, out, out_scale, gate_limit=self.limit)
         if self.shared_size:
-            kernels.stream_add(out, self.shared_expert(h))
+            self.shared_expert(h, out)
         return out

@@ -22,6 +22,21 @@ def linear(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return kernels.gemm(a, w, out)
 
 
+def linear_add(a: torch.Tensor, w: torch.Tensor, into: torch.Tensor) -> torch.Tensor:
+    """into += a . w^T for a float `into` [tokens, out]: the add is the product's epilogue where a kernel has one (the
+    weight-streaming kernels for few tokens, the tcgen05 product for many), else a kernel of its own after the library
+    product.  Either way one float add per element."""
+    if a.shape[0] == 0:
+        return into
+    if kernels.skinny_ok(a.shape[0], w) and a.dtype == torch.bfloat16:
+        kernels.skinny_gemm(w, a.shape[0], act=a, epilogue=kernels.EPI_PLAIN, out=into, accumulate=True)
+    elif kernels.tcgen05_ok(a, w):
+        kernels.gemm_tcgen05(a, w, into, accumulate=True)
+    else:
+        kernels.stream_add(into, linear(a, w))
+    return into
+
+
 def norm_fusable(h, tokens: int, w: torch.Tensor) -> bool:
     """Whether `h` is a pending norm that this product can compute in its own prologue."""
     from .base import PendingNorm

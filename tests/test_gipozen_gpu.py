@@ -110,7 +110,7 @@ def test_rows_of_the_convolved_projections(dtype, hq, hkv, dk, dv, taps, write):
         positions = np.concatenate([np.arange(at[r], at[r] + n, dtype=np.int32) for r, n in zip(batch, sizes)])
         q = torch.full((proj.shape[0], 2 * hq, width), 7.0, dtype=dtype, device="cuda")
         req_slot = dev([slot[r] for r in batch])
-        kernels.diff_rows(proj, conv_w.cuda(), taps, state, token_req=dev(token_req), req_slot=req_slot, q_start=dev(q_start),
+        kernels.diff_rows(proj, conv_w.t().contiguous().cuda(), taps, state, token_req=dev(token_req), req_slot=req_slot, q_start=dev(q_start),
                           positions=dev(positions), q_out=q, k_cache=k_cache if write else None, v_cache=v_cache if write else None,
                           block_table=dev(table), page_size=page, hq=hq, hkv=hkv, key_dim=dk, value_dim=dv)
         kernels.conv_keep(proj, state, req_slot, dev(q_start), dev(sizes), len(batch), taps, channels)
@@ -281,11 +281,14 @@ def test_softmax_router_with_correction(dtype, experts, identity, top, hidden):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("tokens, experts, identity, top, ff, hidden, shared", [
     (1, 4, 2, 2, 40, 72, None), (13, 5, 2, 2, 40, 80, (24, 0.8)), (150, 3, 0, 1, 56, 64, None), (400, 4, 1, 2, 64, 128, (32, 2.0)),
-    (700, 3, 2, 5, 24, 56, (20, 1.0)), (3, 12, 4, 2, 96, 192, (96, 2.0)), (2, 1, 3, 4, 9, 20, None)])
+    (700, 3, 2, 5, 24, 56, (20, 1.0)), (3, 12, 4, 2, 96, 192, (96, 2.0)), (2, 1, 3, 4, 9, 20, None),
+    (512, 2, 1, 2, 200, 128, None), (2048, 4, 0, 2, 520, 128, (64, 1.5))])
 def test_gated_experts_with_identity_and_shared_experts(dtype, tokens, experts, identity, top, ff, hidden, shared):
     """The whole feed-forward part against the plain one with the part's own choice of experts handed to the plain sum (so
     no close call decides): few tokens (a warp per output feature) and many (sorted by expert, grouped tensor-core
-    products in bfloat16), identity experts among the chosen, the shared expert with its per-token factor."""
+    products in bfloat16 with the activation as the first one's epilogue: one column tile, several with a ragged last
+    one, and enough row tiles for the wide tile form), identity experts among the chosen, the shared expert with its
+    per-token factor."""
     g = torch.Generator().manual_seed(tokens + experts)
     limit = 0.7
     shared_spec = {"size": shared[0], "limit": shared[1]} if shared else None
