@@ -39,13 +39,152 @@ template <> __device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloa
     *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(a, b);
 }
 
+constexpr int kSlideTaps = 8;   // most taps whose inputs a lane carries from token to token in registers
+
+// One lane's two neighbouring outputs (channels c0 and c1 of proj; a negative channel is a zero of the padded row) for
+// the n_tok <= CHUNK tokens from t0 on, written where dst(i) points (nullptr: nowhere).  The lane first issues the loads
+// of all its inputs of the run (the tokens' and the taps - 1 before them), so that a warp has a run of loads in flight
+// and not one, and then forms every token's sum from registers.  A token whose bit in `refill` is set (its portion began
+// fewer than taps - 1 tokens before it; with CHUNK 1, every token) is left to a second pass that fetches its inputs from
+// the portion or from the request's kept rows.  Lane i of the warp holds token i's request and place in its portion.
+// The taps are added oldest first in both passes.  TAPS < kSlideTaps: exactly TAPS taps; TAPS == kSlideTaps: `taps` of
+// them, up to kSlideTaps.  Every lane of the warp calls this together.
+template <typename T, int TAPS, int CHUNK, typename Dst>
+__device__ __forceinline__ void conv_pair_run(const float* __restrict__ proj, int row_stride, const float* __restrict__ conv_w,
+                                              const float* __restrict__ state, long long state_stride,
+                                              const int* __restrict__ req_slot, int channels, int taps, int t0, int n_tok,
+                                              unsigned refill, int my_req, int my_local, int c0, int c1, Dst dst) {
+    const int n = TAPS < kSlideTaps ? TAPS : taps;
+    constexpr int HALO = TAPS - 1;
+    float w0[TAPS], w1[TAPS];                              // index j: the weight of the input j tokens back
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) {
+        const bool tap = j < n;
+        w0[j] = tap && c0 >= 0 ? conv_w[(size_t)(n - 1 - j) * channels + c0] : 0.f;
+        w1[j] = tap && c1 >= 0 ? conv_w[(size_t)(n - 1 - j) * channels + c1] : 0.f;
+    }
+    if (CHUNK > 1) {
+        const bool both = c0 >= 0 && c1 == c0 + 1 && ((c0 | row_stride) & 1) == 0 && (reinterpret_cast<uintptr_t>(proj) & 7) == 0;
+        float x0[CHUNK + HALO], x1[CHUNK + HALO];          // index HALO + i: token i's input; below HALO: those before t0
+#pragma unroll
+        for (int k = 0; k < CHUNK + HALO; ++k) {
+            const int i = k - HALO;
+            const bool in = i >= 0 ? i < n_tok : (-i < n && t0 + i >= 0);
+            x0[k] = 0.f; x1[k] = 0.f;
+            if (in && (c0 >= 0 || c1 >= 0)) {
+                const float* row = proj + (size_t)(t0 + i) * row_stride;
+                if (both) {
+                    const float2 v = *reinterpret_cast<const float2*>(row + c0);
+                    x0[k] = v.x; x1[k] = v.y;
+                } else {
+                    if (c0 >= 0) x0[k] = row[c0];
+                    if (c1 >= 0) x1[k] = row[c1];
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < CHUNK; ++i) {
+            if (i < n_tok && !((refill >> i) & 1u)) {
+                float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+                for (int j = TAPS - 1; j >= 0; --j) {
+                    if (j < n) { y0 = fmaf(w0[j], x0[HALO + i - j], y0); y1 = fmaf(w1[j], x1[HALO + i - j], y1); }
+                }
+                T* to = dst(i);
+                if (to != nullptr) store_pair<T>(to, y0, y1);
+            }
+        }
+    }
+    for (unsigned left = refill & (n_tok >= 32 ? 0xffffffffu : (1u << n_tok) - 1u); left != 0; left &= left - 1) {
+        const int i = __ffs(left) - 1;
+        const int req = __shfl_sync(0xffffffffu, my_req, i);
+        const int local = __shfl_sync(0xffffffffu, my_local, i);
+        const float* keep = state + (size_t)req_slot[req] * state_stride;
+        float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+        for (int j = TAPS - 1; j >= 0; --j) {
+            if (j < n) {
+                const int at = local - j;
+                const float* src = at >= 0 ? proj + (size_t)(t0 + i - j) * row_stride : keep + (size_t)(n - 1 + at) * channels;
+                if (c0 >= 0) y0 = fmaf(w0[j], src[c0], y0);
+                if (c1 >= 0) y1 = fmaf(w1[j], src[c1], y1);
+            }
+        }
+        T* to = dst(i);
+        if (to != nullptr) store_pair<T>(to, y0, y1);
+    }
+}
+
 // proj [tokens, row_stride] float; its first `channels` columns are the convolved ones: [q: hq * 2 * dk] and, when
-// write_kv, [k: hkv * 2 * dk][v: hkv * dv].  keep: the request's row of the state tensor, [taps - 1][channels].
-// A warp per row of `width` numbers (2 * hq query rows, then hkv key rows with their value rows), two neighbouring
-// numbers per lane; blockIdx.y shares a token's rows among CTAs where a step has few tokens.  width is even.
+// write_kv, [k: hkv * 2 * dk][v: hkv * dv].  state: a request's row is [taps - 1][channels].
+// A CTA takes `chunk` <= CHUNK neighbouring tokens of the step (of whichever requests).  A warp per row of `width` numbers
+// (2 * hq query rows, then hkv key rows with their value rows), two neighbouring numbers per lane, token after token;
+// blockIdx.y shares the rows among CTAs.  width is even.
+template <typename T, int TAPS, int CHUNK>
+__global__ void __launch_bounds__(256, 3)
+diff_rows_kernel(const float* __restrict__ proj, int row_stride, const float* __restrict__ conv_w, int taps,
+                 const float* __restrict__ state, long long state_stride, const int* __restrict__ token_req,
+                 const int* __restrict__ req_slot, const int* __restrict__ q_start, const int* __restrict__ positions,
+                 T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ block_table,
+                 int table_width, int page_size, int tokens, int chunk, int hq, int hkv, int dk, int dv, int width, int write_kv) {
+    pdl_trigger();
+    const int t0 = blockIdx.x * chunk;
+    const int n_tok = (t0 + chunk < tokens ? t0 + chunk : tokens) - t0;
+    const int nq = hq * 2 * dk, nk = hkv * 2 * dk;
+    const int channels = nq + (write_kv ? nk + hkv * dv : 0);
+    const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int rows = 2 * hq + (write_kv ? hkv : 0);
+    pdl_wait();
+    // lane i learns of token i: its request, its place in the portion and the row of the pages that is its own
+    // (none for a padding row of a fixed-size batch, whose slot has no pages)
+    int my_req = 0, my_local = 0, my_place = -1;
+    if (lane < n_tok) {
+        const int t = t0 + lane;
+        my_req = token_req[t];
+        my_local = t - q_start[my_req];
+        if (write_kv) {
+            const int pos = positions[t];
+            const int page = block_table[(size_t)req_slot[my_req] * table_width + pos / page_size];
+            if (page >= 0) my_place = page * hkv * page_size + pos % page_size;
+        }
+    }
+    const unsigned refill = CHUNK > 1 ? __ballot_sync(0xffffffffu, lane < n_tok && my_local < taps - 1) : 0xffffffffu;
+    for (int row = blockIdx.y * warps + (threadIdx.x >> 5); row < rows; row += gridDim.y * warps) {
+#pragma unroll 1
+        for (int d0 = 0; d0 < width; d0 += 64) {
+            const int d = d0 + 2 * lane;
+            const bool mine = d < width;
+            if (row < 2 * hq) {
+                // query rows: head pair (h, m) is row 2 h + m, its numbers at columns [m * dk, (m + 1) * dk)
+                const int a0 = d - (row & 1) * dk, a1 = a0 + 1;
+                T* to = q_out + ((size_t)t0 * 2 * hq + row) * width + d;
+                const size_t step = (size_t)2 * hq * width;
+                conv_pair_run<T, TAPS, CHUNK>(proj, row_stride, conv_w, state, state_stride, req_slot, channels, taps, t0, n_tok, refill,
+                                       my_req, my_local, mine && a0 >= 0 && a0 < dk ? row * dk + a0 : -1,
+                                       mine && a1 >= 0 && a1 < dk ? row * dk + a1 : -1,
+                                       [&](int i) { return mine ? to + i * step : nullptr; });
+            } else {
+                const int g = row - 2 * hq;
+                const int kc = nq + g * 2 * dk, vc = nq + nk + g * dv;
+                auto place = [&](T* cache, int i) -> T* {
+                    const int at = __shfl_sync(0xffffffffu, my_place, i);
+                    return mine && at >= 0 ? cache + ((size_t)at + (size_t)g * page_size) * width + d : nullptr;
+                };
+                conv_pair_run<T, TAPS, CHUNK>(proj, row_stride, conv_w, state, state_stride, req_slot, channels, taps, t0, n_tok, refill,
+                                       my_req, my_local, mine && d < 2 * dk ? kc + d : -1, mine && d + 1 < 2 * dk ? kc + d + 1 : -1,
+                                       [&](int i) { return place(k_cache, i); });
+                conv_pair_run<T, TAPS, CHUNK>(proj, row_stride, conv_w, state, state_stride, req_slot, channels, taps, t0, n_tok, refill,
+                                       my_req, my_local, mine && d < dv ? vc + d : -1, mine && d + 1 < dv ? vc + d + 1 : -1,
+                                       [&](int i) { return place(v_cache, i); });
+            }
+        }
+    }
+}
+
+// Any number of taps: a CTA per token (blockIdx.y shares its rows), every input fetched for every token that reads it.
 template <typename T>
 __global__ void __launch_bounds__(256)
-diff_rows_kernel(const float* __restrict__ proj, int row_stride, const float* __restrict__ conv_w, int taps,
+diff_rows_long_kernel(const float* __restrict__ proj, int row_stride, const float* __restrict__ conv_w, int taps,
                  const float* __restrict__ state, long long state_stride, const int* __restrict__ token_req,
                  const int* __restrict__ req_slot, const int* __restrict__ q_start, const int* __restrict__ positions,
                  T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ block_table,
@@ -142,6 +281,56 @@ diff_combine_kernel(const T* __restrict__ mixed, const float* __restrict__ gate,
         dst[d] = from_float<T>(o * inv / (1.f + expf(-g[d])));
     }
 }
+
+// The same with two neighbouring numbers per lane and access (dv, width, row_stride and gate_col even): a head's
+// combination stays in registers between the sum of squares and the store, up to kCombineKeep pairs per lane.
+constexpr int kCombineKeep = 4;
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+    static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+};
+template <> struct Pair<__nv_bfloat16> {
+    static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) {
+        return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+diff_combine_pairs_kernel(const T* __restrict__ mixed, const float* __restrict__ gate, int row_stride, int gate_col,
+                          T* __restrict__ out, int tokens, int hq, int dv, int width, float lambda, float eps, float out_scale) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (pair >= tokens * hq) return;
+    const int t = pair / hq, h = pair - t * hq;
+    const T* a1 = mixed + ((size_t)t * 2 * hq + 2 * h) * width;
+    const T* a2 = a1 + width;
+    const float* g = gate + (size_t)t * row_stride + gate_col + h * dv;
+    float2 o[kCombineKeep], gl[kCombineKeep];
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCombineKeep; ++i) {
+        const int d = 2 * lane + 64 * i;
+        o[i] = make_float2(0.f, 0.f); gl[i] = o[i];
+        if (d < dv) {
+            const float2 x = Pair<T>::load(a1 + d), y = Pair<T>::load(a2 + d);
+            gl[i] = *reinterpret_cast<const float2*>(g + d);
+            o[i] = make_float2(x.x - lambda * y.x, x.y - lambda * y.y);
+            sq = fmaf(o[i].x, o[i].x, sq);
+            sq = fmaf(o[i].y, o[i].y, sq);
+        }
+    }
+    sq = warp_sum(sq);
+    const float inv = out_scale / sqrtf(sq / (float)dv + eps);
+    T* dst = out + ((size_t)t * hq + h) * dv;
+#pragma unroll
+    for (int i = 0; i < kCombineKeep; ++i) {
+        const int d = 2 * lane + 64 * i;
+        if (d < dv) store_pair<T>(dst + d, o[i].x * inv / (1.f + expf(-gl[i].x)), o[i].y * inv / (1.f + expf(-gl[i].y)));
+    }
+}
 }  // namespace
 
 CISR_EXPORT int cisr_diff_rows(const float* proj, int row_stride, const float* conv_w, int taps, const float* state,
@@ -152,18 +341,51 @@ CISR_EXPORT int cisr_diff_rows(const float* proj, int row_stride, const float* c
     if (tokens <= 0) return 0;
     if (taps < 1 || width < 2 * dk || width < dv || width % 2 || hq <= 0 || hkv <= 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
-    // eight rows per CTA; as many CTAs per token as bring a small step to about two per SM
+    // eight rows per CTA.  A large step gives a CTA up to sixteen neighbouring tokens, whose inputs it then reads once;
+    // a small one keeps a token per CTA and shares its rows among as many CTAs as bring the launch to about two per SM.
     const int rows = 2 * hq + (write_kv ? hkv : 0);
-    int share = (rows + 7) / 8, want = (296 + tokens - 1) / tokens;
-    share = share < want ? share : want;
-    const dim3 grid(tokens, share < 1 ? 1 : share);
-    if (dtype == CISR_BF16)
-        return launch_kernel(diff_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, g_pdl, proj, row_stride, conv_w, taps, state,
-                             state_stride, token_req, req_slot, q_start, positions, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
-                             (__nv_bfloat16*)v_cache, block_table, table_width, page_size, hq, hkv, dk, dv, width, write_kv);
-    return launch_kernel(diff_rows_kernel<float>, grid, dim3(256), 0, s, g_pdl, proj, row_stride, conv_w, taps, state, state_stride,
-                         token_req, req_slot, q_start, positions, (float*)q_out, (float*)k_cache, (float*)v_cache, block_table,
-                         table_width, page_size, hq, hkv, dk, dv, width, write_kv);
+    int share = (rows + 7) / 8;
+    if (taps > kSlideTaps) {
+        const int want = (296 + tokens - 1) / tokens;
+        const dim3 grid(tokens, share < want ? share : want);
+        if (dtype == CISR_BF16)
+            return launch_kernel(diff_rows_long_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, g_pdl, proj, row_stride, conv_w, taps,
+                                 state, state_stride, token_req, req_slot, q_start, positions, (__nv_bfloat16*)q_out,
+                                 (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, block_table, table_width, page_size, hq, hkv, dk, dv,
+                                 width, write_kv);
+        return launch_kernel(diff_rows_long_kernel<float>, grid, dim3(256), 0, s, g_pdl, proj, row_stride, conv_w, taps, state,
+                             state_stride, token_req, req_slot, q_start, positions, (float*)q_out, (float*)k_cache, (float*)v_cache,
+                             block_table, table_width, page_size, hq, hkv, dk, dv, width, write_kv);
+    }
+    long long chunk = (long long)tokens * share / 592;
+    chunk = chunk > 16 ? 16 : chunk < 1 ? 1 : chunk;
+    if (chunk == 1) {
+        const int want = (296 + tokens - 1) / tokens;
+        share = share < want ? share : want;
+    }
+    const dim3 grid((unsigned)((tokens + chunk - 1) / chunk), share < 1 ? 1 : share);
+#define CISR_DIFF_ROWS_OF(TAPS, CHUNK)                                                                                          \
+    return dtype == CISR_BF16                                                                                                   \
+        ? launch_kernel(diff_rows_kernel<__nv_bfloat16, TAPS, CHUNK>, grid, dim3(256), 0, s, g_pdl, proj, row_stride, conv_w,   \
+                        taps, state, state_stride, token_req, req_slot, q_start, positions, (__nv_bfloat16*)q_out,              \
+                        (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, block_table, table_width, page_size, tokens,          \
+                        (int)chunk, hq, hkv, dk, dv, width, write_kv)                                                           \
+        : launch_kernel(diff_rows_kernel<float, TAPS, CHUNK>, grid, dim3(256), 0, s, g_pdl, proj, row_stride, conv_w, taps,     \
+                        state, state_stride, token_req, req_slot, q_start, positions, (float*)q_out, (float*)k_cache,           \
+                        (float*)v_cache, block_table, table_width, page_size, tokens, (int)chunk, hq, hkv, dk, dv, width,       \
+                        write_kv)
+#define CISR_DIFF_ROWS(TAPS)                        \
+    if (chunk > 1) { CISR_DIFF_ROWS_OF(TAPS, 16); } \
+    CISR_DIFF_ROWS_OF(TAPS, 1)
+    switch (taps) {
+        case 1: CISR_DIFF_ROWS(1);
+        case 2: CISR_DIFF_ROWS(2);
+        case 3: CISR_DIFF_ROWS(3);
+        case 4: CISR_DIFF_ROWS(4);
+        default: CISR_DIFF_ROWS(kSlideTaps);
+    }
+#undef CISR_DIFF_ROWS
+#undef CISR_DIFF_ROWS_OF
 }
 
 CISR_EXPORT int cisr_conv_keep(const float* proj, int row_stride, float* state, long long state_stride, const int* req_slot,
@@ -179,6 +401,17 @@ CISR_EXPORT int cisr_diff_combine(const void* mixed, const float* gate, int row_
     if (tokens <= 0) return 0;
     const int pairs = tokens * hq;
     cudaStream_t s = (cudaStream_t)stream;
+    const bool even = ((dv | width | row_stride | gate_col) & 1) == 0 && dv <= 64 * kCombineKeep &&
+                      ((reinterpret_cast<uintptr_t>(mixed) | reinterpret_cast<uintptr_t>(out)) & 7) == 0 &&
+                      (reinterpret_cast<uintptr_t>(gate) & 7) == 0;
+    if (even) {
+        if (dtype == CISR_BF16)
+            return launch_kernel(diff_combine_pairs_kernel<__nv_bfloat16>, dim3((pairs + 7) / 8), dim3(256), 0, s, g_pdl,
+                                 (const __nv_bfloat16*)mixed, gate, row_stride, gate_col, (__nv_bfloat16*)out, tokens, hq, dv, width,
+                                 lambda, eps, out_scale);
+        return launch_kernel(diff_combine_pairs_kernel<float>, dim3((pairs + 7) / 8), dim3(256), 0, s, g_pdl, (const float*)mixed, gate,
+                             row_stride, gate_col, (float*)out, tokens, hq, dv, width, lambda, eps, out_scale);
+    }
     if (dtype == CISR_BF16)
         return launch_kernel(diff_combine_kernel<__nv_bfloat16>, dim3((pairs + 3) / 4), dim3(128), 0, s, g_pdl, (const __nv_bfloat16*)mixed,
                              gate, row_stride, gate_col, (__nv_bfloat16*)out, tokens, hq, dv, width, lambda, eps, out_scale);

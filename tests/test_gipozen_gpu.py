@@ -144,7 +144,74 @@ def test_rows_of_the_convolved_projections(dtype, hq, hkv, dk, dv, taps, write):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("tokens, hq, dv, width", [(5, 4, 40, 48), (130, 2, 96, 128), (3, 3, 12, 32), (64, 1, 25, 32), (9, 8, 64, 64)])
+@pytest.mark.parametrize("hq, hkv, dk, dv, taps, first, second", [
+    (16, 4, 8, 16, 4, [900, 1, 2, 1100], [1, 1500, 3, 500]),     # sixteen tokens per CTA
+    (4, 2, 24, 40, 3, [400, 2, 1, 300], [2, 5, 350, 1]),          # a few tokens per CTA
+    (16, 4, 7, 16, 8, [1000, 3, 1000], [7, 6, 2000]),             # as many taps as a lane carries; an odd key width
+    (16, 4, 8, 16, 9, [1000, 3, 1000], [7, 6, 2000]),             # more taps than a lane carries
+    (16, 4, 8, 16, 1, [1000, 3, 1000], [7, 6, 2000])])
+def test_rows_of_a_large_step(dtype, hq, hkv, dk, dv, taps, first, second):
+    """A step of many tokens gives a CTA several neighbouring tokens, of whichever requests: portions that begin in the
+    middle of a CTA's tokens, portions shorter than the taps beside long ones, and a second step that goes on from the
+    kept inputs of the first."""
+    from cisr_b200.ops import kernels
+    g = torch.Generator().manual_seed(taps * 10 + hq)
+    width = -(-max(2 * dk, dv) // 16) * 16
+    nq, nk, nv = hq * 2 * dk, hkv * 2 * dk, hkv * dv
+    channels = nq + nk + nv
+    conv_w = torch.randn(channels, taps, generator=g)
+    lengths = [a + b for a, b in zip(first, second)]
+    us = [torch.randn(n, channels + 3, generator=g) for n in lengths]
+    want = [pg.causal_conv(u[:, :channels].to(F), conv_w.to(F)) for u in us]
+    page = 16
+    per = [-(-n // page) for n in lengths]
+    n_pages = sum(per)
+    order = torch.randperm(n_pages, generator=g).numpy().astype(np.int32)
+    table = np.full((len(lengths), max(per)), -1, dtype=np.int32)
+    used = 0
+    for r, n in enumerate(per):
+        table[r, :n] = order[used:used + n]
+        used += n
+    state = torch.zeros(len(lengths), max(taps - 1, 1), channels).cuda()
+    k_cache = torch.zeros(n_pages, hkv, page, width, dtype=dtype, device="cuda")
+    v_cache = torch.zeros_like(k_cache)
+    at, got = [0] * len(lengths), [[] for _ in lengths]
+    for sizes in (first, second):
+        proj = torch.cat([us[r][at[r]:at[r] + n] for r, n in enumerate(sizes)]).cuda().contiguous()
+        q_start = np.cumsum([0] + sizes[:-1]).astype(np.int32)
+        token_req = np.concatenate([np.full(n, r, dtype=np.int32) for r, n in enumerate(sizes)])
+        positions = np.concatenate([np.arange(at[r], at[r] + n, dtype=np.int32) for r, n in enumerate(sizes)])
+        q = torch.full((proj.shape[0], 2 * hq, width), 7.0, dtype=dtype, device="cuda")
+        req_slot = dev(np.arange(len(sizes)))
+        kernels.diff_rows(proj, conv_w.t().contiguous().cuda(), taps, state, token_req=dev(token_req), req_slot=req_slot,
+                          q_start=dev(q_start), positions=dev(positions), q_out=q, k_cache=k_cache, v_cache=v_cache,
+                          block_table=dev(table), page_size=page, hq=hq, hkv=hkv, key_dim=dk, value_dim=dv)
+        kernels.conv_keep(proj, state, req_slot, dev(q_start), dev(sizes), len(sizes), taps, channels)
+        for r, n in enumerate(sizes):
+            got[r].append(q[q_start[r]:q_start[r] + n].float().cpu())
+            at[r] += n
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    for r, n in enumerate(lengths):
+        q = torch.cat(got[r]).view(n, hq, 2, width)
+        ref = want[r][:, :nq].view(n, hq, 2, dk)
+        for m in (0, 1):
+            assert (q[:, :, m, m * dk:(m + 1) * dk].to(F) - ref[:, :, m]).abs().max() < tol * ref.abs().max()
+            outside = torch.ones(width, dtype=torch.bool)
+            outside[m * dk:(m + 1) * dk] = False
+            assert float(q[:, :, m, outside].abs().max()) == 0.0
+        pages = torch.tensor(table[r][:per[r]].astype(np.int64))
+        k = k_cache[pages].float().cpu().permute(0, 2, 1, 3).reshape(-1, hkv, width)[:n]
+        v = v_cache[pages].float().cpu().permute(0, 2, 1, 3).reshape(-1, hkv, width)[:n]
+        ref_k = want[r][:, nq:nq + nk].view(n, hkv, 2 * dk)
+        ref_v = want[r][:, nq + nk:].view(n, hkv, dv)
+        assert (k[:, :, :2 * dk].to(F) - ref_k).abs().max() < tol * ref_k.abs().max()
+        assert (v[:, :, :dv].to(F) - ref_v).abs().max() < tol * ref_v.abs().max()
+        assert float(k[:, :, 2 * dk:].abs().sum()) == 0.0 and float(v[:, :, dv:].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens, hq, dv, width", [(5, 4, 40, 48), (130, 2, 96, 128), (3, 3, 12, 32), (64, 1, 25, 32), (9, 8, 64, 64),
+                                                   (7, 2, 320, 320), (33, 2, 250, 256)])
 def test_combination_of_the_two_maps(dtype, tokens, hq, dv, width):
     from cisr_b200.ops import kernels
     g = torch.Generator().manual_seed(tokens + dv)
