@@ -42,7 +42,7 @@ template <> __device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloa
 constexpr int kSlideTaps = 8;   // most taps whose inputs a lane carries from token to token in registers
 
 // One lane's two neighbouring outputs (channels c0 and c1 of proj; a negative channel is a zero of the padded row) for
-// the n_tok <= CHUNK tokens from t0 on, written where dst(i) points (nullptr: nowhere).  The lane first issues the loads
+// the n_tok <= CHUNK tokens from t0 on, handed to dst(i, y0, y1), which stores them.  The lane first issues the loads
 // of all its inputs of the run (the tokens' and the taps - 1 before them), so that a warp has a run of loads in flight
 // and not one, and then forms every token's sum from registers.  A token whose bit in `refill` is set (its portion began
 // fewer than taps - 1 tokens before it; with CHUNK 1, every token) is left to a second pass that fetches its inputs from
@@ -90,8 +90,7 @@ __device__ __forceinline__ void conv_pair_run(const float* __restrict__ proj, in
                 for (int j = TAPS - 1; j >= 0; --j) {
                     if (j < n) { y0 = fmaf(w0[j], x0[HALO + i - j], y0); y1 = fmaf(w1[j], x1[HALO + i - j], y1); }
                 }
-                T* to = dst(i);
-                if (to != nullptr) store_pair<T>(to, y0, y1);
+                dst(i, y0, y1);
             }
         }
     }
@@ -110,16 +109,15 @@ __device__ __forceinline__ void conv_pair_run(const float* __restrict__ proj, in
                 if (c1 >= 0) y1 = fmaf(w1[j], src[c1], y1);
             }
         }
-        T* to = dst(i);
-        if (to != nullptr) store_pair<T>(to, y0, y1);
+        dst(i, y0, y1);
     }
 }
 
 // proj [tokens, row_stride] float; its first `channels` columns are the convolved ones: [q: hq * 2 * dk] and, when
 // write_kv, [k: hkv * 2 * dk][v: hkv * dv].  state: a request's row is [taps - 1][channels].
-// A CTA takes `chunk` <= CHUNK neighbouring tokens of the step (of whichever requests).  A warp per row of `width` numbers
-// (2 * hq query rows, then hkv key rows with their value rows), two neighbouring numbers per lane, token after token;
-// blockIdx.y shares the rows among CTAs.  width is even.
+// A CTA takes `chunk` <= CHUNK neighbouring tokens of the step (of whichever requests).  A warp per run of `width` columns
+// (the query rows, then hkv key rows with their value rows), two neighbouring numbers per lane, token after token;
+// blockIdx.y shares the runs among CTAs.  width is even.
 template <typename T, int TAPS, int CHUNK>
 __global__ void __launch_bounds__(256, 3)
 diff_rows_kernel(const float* __restrict__ proj, int row_stride, const float* __restrict__ conv_w, int taps,
@@ -133,7 +131,10 @@ diff_rows_kernel(const float* __restrict__ proj, int row_stride, const float* __
     const int nq = hq * 2 * dk, nk = hkv * 2 * dk;
     const int channels = nq + (write_kv ? nk + hkv * dv : 0);
     const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    const int rows = 2 * hq + (write_kv ? hkv : 0);
+    // with an even dk one run of a warp makes both maps' rows of a head (their channels are neighbours in proj)
+    const bool packed = (dk & 1) == 0;
+    const int q_runs = packed ? hq : 2 * hq;
+    const int rows = q_runs + (write_kv ? hkv : 0);
     pdl_wait();
     // lane i learns of token i: its request, its place in the portion and the row of the pages that is its own
     // (none for a padding row of a fixed-size batch, whose slot has no pages)
@@ -149,33 +150,47 @@ diff_rows_kernel(const float* __restrict__ proj, int row_stride, const float* __
         }
     }
     const unsigned refill = CHUNK > 1 ? __ballot_sync(0xffffffffu, lane < n_tok && my_local < taps - 1) : 0xffffffffu;
+    const size_t step = (size_t)2 * hq * width;            // from a token's query rows to the next token's
     for (int row = blockIdx.y * warps + (threadIdx.x >> 5); row < rows; row += gridDim.y * warps) {
 #pragma unroll 1
         for (int d0 = 0; d0 < width; d0 += 64) {
             const int d = d0 + 2 * lane;
             const bool mine = d < width;
-            if (row < 2 * hq) {
+            if (row < q_runs && packed) {
+                // head `row`: column d < dk belongs to map 1 (query row 2 h), dk <= d < 2 dk to map 2 (row 2 h + 1); the
+                // lane writes its numbers into the row of their map and zeros into the other row's same columns
+                const bool real = mine && d < 2 * dk;
+                const int m = real && d >= dk ? 1 : 0;
+                T* value = q_out + ((size_t)t0 * 2 * hq + 2 * row + m) * width + d;
+                T* zeros = q_out + ((size_t)t0 * 2 * hq + 2 * row + 1 - m) * width + d;
+                conv_pair_run<T, TAPS, CHUNK>(proj, row_stride, conv_w, state, state_stride, req_slot, channels, taps, t0, n_tok, refill,
+                                              my_req, my_local, real ? 2 * row * dk + d : -1, real ? 2 * row * dk + d + 1 : -1,
+                                              [&](int i, float y0, float y1) {
+                                                  if (!mine) return;
+                                                  store_pair<T>(value + i * step, y0, y1);
+                                                  store_pair<T>(zeros + i * step, 0.f, 0.f);
+                                              });
+            } else if (row < q_runs) {
                 // query rows: head pair (h, m) is row 2 h + m, its numbers at columns [m * dk, (m + 1) * dk)
                 const int a0 = d - (row & 1) * dk, a1 = a0 + 1;
                 T* to = q_out + ((size_t)t0 * 2 * hq + row) * width + d;
-                const size_t step = (size_t)2 * hq * width;
                 conv_pair_run<T, TAPS, CHUNK>(proj, row_stride, conv_w, state, state_stride, req_slot, channels, taps, t0, n_tok, refill,
-                                       my_req, my_local, mine && a0 >= 0 && a0 < dk ? row * dk + a0 : -1,
-                                       mine && a1 >= 0 && a1 < dk ? row * dk + a1 : -1,
-                                       [&](int i) { return mine ? to + i * step : nullptr; });
+                                              my_req, my_local, mine && a0 >= 0 && a0 < dk ? row * dk + a0 : -1,
+                                              mine && a1 >= 0 && a1 < dk ? row * dk + a1 : -1,
+                                              [&](int i, float y0, float y1) { if (mine) store_pair<T>(to + i * step, y0, y1); });
             } else {
-                const int g = row - 2 * hq;
+                const int g = row - q_runs;
                 const int kc = nq + g * 2 * dk, vc = nq + nk + g * dv;
-                auto place = [&](T* cache, int i) -> T* {
+                auto place = [&](T* cache, int i, float y0, float y1) {
                     const int at = __shfl_sync(0xffffffffu, my_place, i);
-                    return mine && at >= 0 ? cache + ((size_t)at + (size_t)g * page_size) * width + d : nullptr;
+                    if (mine && at >= 0) store_pair<T>(cache + ((size_t)at + (size_t)g * page_size) * width + d, y0, y1);
                 };
                 conv_pair_run<T, TAPS, CHUNK>(proj, row_stride, conv_w, state, state_stride, req_slot, channels, taps, t0, n_tok, refill,
-                                       my_req, my_local, mine && d < 2 * dk ? kc + d : -1, mine && d + 1 < 2 * dk ? kc + d + 1 : -1,
-                                       [&](int i) { return place(k_cache, i); });
+                                              my_req, my_local, mine && d < 2 * dk ? kc + d : -1, mine && d + 1 < 2 * dk ? kc + d + 1 : -1,
+                                              [&](int i, float y0, float y1) { place(k_cache, i, y0, y1); });
                 conv_pair_run<T, TAPS, CHUNK>(proj, row_stride, conv_w, state, state_stride, req_slot, channels, taps, t0, n_tok, refill,
-                                       my_req, my_local, mine && d < dv ? vc + d : -1, mine && d + 1 < dv ? vc + d + 1 : -1,
-                                       [&](int i) { return place(v_cache, i); });
+                                              my_req, my_local, mine && d < dv ? vc + d : -1, mine && d + 1 < dv ? vc + d + 1 : -1,
+                                              [&](int i, float y0, float y1) { place(v_cache, i, y0, y1); });
             }
         }
     }
@@ -343,8 +358,7 @@ CISR_EXPORT int cisr_diff_rows(const float* proj, int row_stride, const float* c
     cudaStream_t s = (cudaStream_t)stream;
     // eight rows per CTA.  A large step gives a CTA up to sixteen neighbouring tokens, whose inputs it then reads once;
     // a small one keeps a token per CTA and shares its rows among as many CTAs as bring the launch to about two per SM.
-    const int rows = 2 * hq + (write_kv ? hkv : 0);
-    int share = (rows + 7) / 8;
+    int share = (2 * hq + (write_kv ? hkv : 0) + 7) / 8;
     if (taps > kSlideTaps) {
         const int want = (296 + tokens - 1) / tokens;
         const dim3 grid(tokens, share < want ? share : want);
@@ -357,6 +371,7 @@ CISR_EXPORT int cisr_diff_rows(const float* proj, int row_stride, const float* c
                              state_stride, token_req, req_slot, q_start, positions, (float*)q_out, (float*)k_cache, (float*)v_cache,
                              block_table, table_width, page_size, hq, hkv, dk, dv, width, write_kv);
     }
+    share = (((dk & 1) == 0 ? hq : 2 * hq) + (write_kv ? hkv : 0) + 7) / 8;   // an even dk: a run per head makes both maps' rows
     long long chunk = (long long)tokens * share / 592;
     chunk = chunk > 16 ? 16 : chunk < 1 ? 1 : chunk;
     if (chunk == 1) {
