@@ -327,7 +327,7 @@ def expert_tensors(g, hidden, ff, experts, identity, shared, correction=0.2):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("experts, identity, top, hidden", [(5, 2, 2, 80), (3, 0, 1, 72), (12, 4, 2, 192), (4, 1, 5, 64), (1, 3, 2, 40), (16, 0, 4, 128)])
+@pytest.mark.parametrize("experts, identity, top, hidden", [(5, 2, 2, 80), (3, 0, 1, 72), (10, 3, 2, 176), (4, 1, 5, 64), (1, 3, 2, 40), (16, 0, 4, 128)])
 def test_softmax_router_with_correction(dtype, experts, identity, top, hidden):
     """The choice is made by score + correction and the weights are the scores without it: the corrections are drawn
     wide enough that they change the choice for many tokens (checked), inputs equal to the bit."""
@@ -348,7 +348,7 @@ def test_softmax_router_with_correction(dtype, experts, identity, top, hidden):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("tokens, experts, identity, top, ff, hidden, shared", [
     (1, 4, 2, 2, 40, 72, None), (13, 5, 2, 2, 40, 80, (24, 0.8)), (150, 3, 0, 1, 56, 64, None), (400, 4, 1, 2, 64, 128, (32, 2.0)),
-    (700, 3, 2, 5, 24, 56, (20, 1.0)), (3, 12, 4, 2, 96, 192, (96, 2.0)), (2, 1, 3, 4, 9, 20, None),
+    (700, 3, 2, 5, 24, 56, (20, 1.0)), (3, 10, 3, 2, 80, 176, (48, 2.0)), (2, 1, 3, 4, 9, 20, None),
     (512, 2, 1, 2, 200, 128, None), (2048, 4, 0, 2, 520, 128, (64, 1.5))])
 def test_gated_experts_with_identity_and_shared_experts(dtype, tokens, experts, identity, top, ff, hidden, shared):
     """The whole feed-forward part against the plain one with the part's own choice of experts handed to the plain sum (so
