@@ -6,8 +6,9 @@ from .llama import LlamaConfig      # registers LlamaForCausalLM
 from .zurolorn import ZurolornConfig    # registers Zurolorn
 from .ronolorn import RonolornConfig    # registers Ronolorn
 from .gipozen import GipozenConfig      # registers Gipozen
+from .vilodra import VilodraConfig      # registers Vilodra
 from .presets import preset, preset_dict, preset_names
 
-__all__ = ["CacheUse", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "LlamaConfig", "ZurolornConfig", "RonolornConfig", "GipozenConfig",
+__all__ = ["CacheUse", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "LlamaConfig", "ZurolornConfig", "RonolornConfig", "GipozenConfig", "VilodraConfig",
            "ARCHITECTURES", "Architecture", "architecture_for", "register_architecture",
            "preset", "preset_dict", "preset_names"]

@@ -69,7 +69,8 @@ attn_prefill_kernel(const st_t* __restrict__ q, st_t* __restrict__ out, const st
                     const st_t* __restrict__ v_cache, const int* __restrict__ req_slot,
                     const int* __restrict__ block_table, int table_width, const int* __restrict__ tile_req, const int* __restrict__ tile_q0,
                     const int* __restrict__ q_start, const int* __restrict__ q_len,
-                    const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window, int keep_first, float sink) {
+                    const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window, int keep_first, float sink,
+                    const float* __restrict__ sink_heads) {
     CISR_TRACE_SCOPE(TRACE_ATTN_SIMT);
     extern __shared__ __align__(16) float smem[];
     float* Qs = smem;             // [D][QS]   transposed, pre-scaled
@@ -208,8 +209,9 @@ attn_prefill_kernel(const st_t* __restrict__ q, st_t* __restrict__ out, const st
     for (int i = 0; i < 4; ++i) {
         const int r = ty * 4 + i;
         if (r >= rows) continue;
-        // a sink is one more term of the denominator, exp(sink), with no value (sink -inf: none)
-        const float inv = 1.f / (sink > -INFINITY ? l_run[i] + expf(sink - m_run[i]) : l_run[i]);
+        // a sink is one more term of the denominator, exp(sink), with no value (sink -inf: none); one per head where given
+        const float sk = sink_heads ? sink_heads[head] : sink;
+        const float inv = 1.f / (sk > -INFINITY ? l_run[i] + expf(sk - m_run[i]) : l_run[i]);
         st_t* dst = out + ((size_t)(tok0 + r) * hq + head) * D;
 #pragma unroll
         for (int j = 0; j < ND; ++j) dst[tx + 16 * j] = from_float<st_t>(o[i][j] * inv);
@@ -364,9 +366,11 @@ attn_decode_kernel(const st_t* __restrict__ q, const st_t* __restrict__ k_cache,
 
 __global__ void attn_merge_kernel(const float* __restrict__ partial, const float* __restrict__ stats,
                                   st_t* __restrict__ out, const int* __restrict__ dec_req,
-                                  const int* __restrict__ q_start, int hq, int n_splits, float sink) {
+                                  const int* __restrict__ q_start, int hq, int n_splits, float sink_all,
+                                  const float* __restrict__ sink_heads) {
     CISR_TRACE_SCOPE(TRACE_ATTN_MERGE);
     const int slot = blockIdx.x, head = blockIdx.y;
+    const float sink = sink_heads ? sink_heads[head] : sink_all;
     const size_t base = ((size_t)slot * hq + head) * n_splits;
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s)
@@ -395,7 +399,8 @@ CISR_EXPORT int cisr_attn_prefill_tile() { return BM; }
 CISR_EXPORT int cisr_attn_prefill(const void* q, void* out, const void* k_cache, const void* v_cache,
                                   const int* req_slot, const int* block_table, int table_width, const int* tile_req, const int* tile_q0,
                                   int n_tiles, const int* q_start, const int* q_len, const int* ctx_len, int hq,
-                                  int hkv, int page_size, float scale, int window, int keep_first, float sink, void* stream) {
+                                  int hkv, int page_size, float scale, int window, int keep_first, float sink, const float* sink_heads,
+                                  void* stream) {
     if (n_tiles <= 0) return 0;
     if (hq % hkv) return -2;
     static bool configured = false;
@@ -406,7 +411,7 @@ CISR_EXPORT int cisr_attn_prefill(const void* q, void* out, const void* k_cache,
     }
     attn_prefill_kernel<<<dim3(n_tiles, hq), PREFILL_THREADS, PREFILL_SMEM, (cudaStream_t)stream>>>(
         (const st_t*)q, (st_t*)out, (const st_t*)k_cache, (const st_t*)v_cache, req_slot, block_table, table_width, tile_req,
-        tile_q0, q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, keep_first, sink);
+        tile_q0, q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, keep_first, sink, sink_heads);
     return launch_status();
 }
 
@@ -415,7 +420,7 @@ CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, 
                                  const int* req_slot, const int* block_table, int table_width, const int* dec_req, int n_dec,
                                  const int* q_start, const int* ctx_len, float* partial, float* stats, int hq,
                                  int hkv, int page_size, float scale, int window, int keep_first, int split_size, int n_splits,
-                                 float sink, void* stream) {
+                                 float sink, const float* sink_heads, void* stream) {
     if (n_dec <= 0) return 0;
     if (hq % hkv || split_size <= 0 || n_splits <= 0) return -2;
     const size_t smem = decode_smem_floats(hq / hkv) * sizeof(float);
@@ -432,6 +437,6 @@ CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, 
         ctx_len, partial, stats, hq, hkv, page_size, scale, window, keep_first, split_size, n_splits);
     int status = launch_status();
     if (status) return status;
-    attn_merge_kernel<<<dim3(n_dec, hq), D < 128 ? 64 : 128, 0, s>>>(partial, stats, (st_t*)out, dec_req, q_start, hq, n_splits, sink);
+    attn_merge_kernel<<<dim3(n_dec, hq), D < 128 ? 64 : 128, 0, s>>>(partial, stats, (st_t*)out, dec_req, q_start, hq, n_splits, sink, sink_heads);
     return launch_status();
 }

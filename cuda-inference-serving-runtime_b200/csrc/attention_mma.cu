@@ -120,7 +120,8 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
                         const bf16* __restrict__ v_cache, const int* __restrict__ req_slot,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ tile_req,
                         const int* __restrict__ tile_q0, const int* __restrict__ q_start, const int* __restrict__ q_len,
-                        const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window, int keep_first, float sink) {
+                        const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window, int keep_first, float sink_all,
+                        const float* __restrict__ sink_heads) {
     CISR_TRACE_SCOPE(TRACE_ATTN_PREFILL);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][LDS]
@@ -327,6 +328,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
             }
         }
         if (row < rows) {
+            const float sink = sink_heads ? sink_heads[head] : sink_all;     // one per head where given
             if (sink > -INFINITY) l += exp2f(sink * LOG2E - m_use);     // the sink: one more term of the denominator, no value
             const float inv = 1.f / l;
             bf16* dst = out + ((size_t)(tok0 + row) * hq + head) * D + 2 * (lane & 3);
@@ -905,12 +907,14 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 // are computed once into shared memory and the sum runs over the ranges in their fixed order.
 __global__ void attn_merge_kernel(const float* __restrict__ partial, const float* __restrict__ stats,
                                   bf16* __restrict__ out, const int* __restrict__ dec_req,
-                                  const int* __restrict__ q_start, int hq, int n_splits, float sink) {
+                                  const int* __restrict__ q_start, int hq, int n_splits, float sink_all,
+                                  const float* __restrict__ sink_heads) {
     CISR_TRACE_SCOPE(TRACE_ATTN_MERGE);
     extern __shared__ float weights[];            // [n_splits] weights, then [n_splits] weighted denominators
     __shared__ float scratch[32];
     pdl_trigger();
     const int slot = blockIdx.x, head = blockIdx.y;
+    const float sink = sink_heads ? sink_heads[head] : sink_all;     // one per head where given; neither comes from the kernel before
     const size_t base = ((size_t)slot * hq + head) * n_splits;
     const int tok = q_start[dec_req[slot]];       // request metadata does not come from the kernel before
     pdl_wait();
@@ -971,7 +975,7 @@ CISR_EXPORT int cisr_attn_prefill(const void* q, void* out, const void* k_cache,
                                   const int* req_slot, const int* block_table, int table_width, const int* tile_req,
                                   const int* tile_q0, int n_tiles, const int* q_start, const int* q_len,
                                   const int* ctx_len, int hq, int hkv, int page_size, float scale, int window,
-                                  int keep_first, float sink, void* stream) {
+                                  int keep_first, float sink, const float* sink_heads, void* stream) {
     if (n_tiles <= 0) return 0;
     if (hq % hkv) return -2;
     const size_t smem = PREFILL_SMEM + sizeof(int) * ((size_t)table_width + 4);    // a tile's key range spans at most the table
@@ -984,14 +988,14 @@ CISR_EXPORT int cisr_attn_prefill(const void* q, void* out, const void* k_cache,
     }
     return launch_kernel(attn_prefill_mma_kernel, dim3(n_tiles, hq), dim3(PREFILL_THREADS), smem, (cudaStream_t)stream, g_pdl,
                          (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, req_slot, block_table,
-                         table_width, tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, keep_first, sink);
+                         table_width, tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, keep_first, sink, sink_heads);
 }
 
 CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
                                  const int* req_slot, const int* block_table, int table_width, const int* dec_req,
                                  int n_dec, const int* q_start, const int* ctx_len, float* partial, float* stats, int hq,
                                  int hkv, int page_size, float scale, int window, int keep_first, int split_size, int n_splits,
-                                 int merge, float sink, void* stream) {
+                                 int merge, float sink, const float* sink_heads, void* stream) {
     // merge == 0: the ranges' partial sums and statistics are left in `partial` and `stats` for the caller's own merge
     // (merge_proj.cu merges them in the prologue of the output projection); `out` is then not written.
     if (n_dec <= 0) return 0;
@@ -1015,7 +1019,7 @@ CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, 
     }
     if (!merge) return 0;
     return launch_kernel(attn_merge_kernel, dim3(n_dec, hq), dim3(D <= 64 ? 64 : 128), sizeof(float) * 2 * (size_t)n_splits, s, g_pdl,
-                         (const float*)partial, (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_splits, sink);
+                         (const float*)partial, (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_splits, sink, sink_heads);
 }
 
 // 1 when this library has the variant that stages tiles by tensor-map copies, and it takes this page and range size.
@@ -1045,7 +1049,7 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
                                      const int* req_slot, const int* block_table, int table_width, const int* dec_req,
                                      int n_dec, const int* q_start, const int* ctx_len, float* partial, float* stats,
                                      int hq, int hkv, int page_size, float scale, int window, int keep_first, int split_size,
-                                     int n_splits, int merge, float sink, void* stream) {
+                                     int n_splits, int merge, float sink, const float* sink_heads, void* stream) {
     // `sink` (-inf: none) is added to the denominator by the merge kernel, so the ranges are never merged inside a cluster then
     if (n_dec <= 0) return 0;
     if (!g_encode || !g_error) return -13;
@@ -1080,7 +1084,7 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
     int cluster = 1;
     size_t smem = smem_plain;
     static int resident[17] = {};            // per cluster size: 0 unknown, 1 yes, -1 no (asked with the largest shared memory)
-    for (int c = 16; c >= 2 && g_clusters && !(sink > -INFINITY); --c) {
+    for (int c = 16; c >= 2 && g_clusters && !(sink > -INFINITY) && !sink_heads; --c) {
         if (n_splits % c) continue;
         const size_t need = smem_plain + sizeof(float) * (size_t)c * rows_max * ((D + c - 1) / c + 2);
         if (need > SMEM_CAP) continue;
@@ -1124,7 +1128,7 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
     }
     if ((n_parts == 1 && cluster > 1) || !merge) return 0;
     return launch_kernel(attn_merge_kernel, dim3(n_dec, hq), dim3(D <= 64 ? 64 : 128), sizeof(float) * 2 * (size_t)n_parts, s, g_pdl,
-                         (const float*)partial, (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_parts, sink);
+                         (const float*)partial, (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_parts, sink, sink_heads);
 }
 
 #ifdef DEC_TRACE

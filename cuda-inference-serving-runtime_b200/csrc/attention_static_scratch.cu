@@ -62,5 +62,5 @@ int cisr_attn_decode_static(const void* q, void* out, const void* k_cache, const
     float* stats = partial + cells * D;                // [n_dec, hq, n_splits, 2]
     return cisr_attn_decode(q, out, k_cache, v_cache, req_slot, block_table, table_width, dec_req, n_dec, q_start,
                             ctx_len, partial, stats, hq, hkv, page_size, scale, window, 0 /* no kept first keys */, split_size, n_splits,
-                            -INFINITY /* no sink */, stream);
+                            -INFINITY /* no sink */, nullptr /* nor one per head */, stream);
 }

@@ -79,7 +79,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ tile_req, const int* __restrict__ tile_q0,
                             const int* __restrict__ q_start, const int* __restrict__ q_len,
                             const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window,
-                            int keep_first, float sink, int* __restrict__ error) {
+                            int keep_first, float sink_all, const float* __restrict__ sink_heads, int* __restrict__ error) {
     CISR_TRACE_SCOPE(TRACE_ATTN_PREFILL);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -370,6 +370,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const float m0 = exchange[row], m1 = exchange[BM + row], m = fmaxf(m0, m1);
             const float w0 = m0 == -INFINITY ? 0.f : fast_exp2(m0 - m), w1 = m1 == -INFINITY ? 0.f : fast_exp2(m1 - m);
             float total = exchange[2 * BM + row] * w0 + exchange[3 * BM + row] * w1;
+            const float sink = sink_heads ? sink_heads[head] : sink_all;     // one per head where given
             if (total > 0.f && sink > -INFINITY) total += exp2f(sink * LOG2E - m);   // the sink: one more term of the denominator, no value
             const float inv = total > 0.f ? 1.f / total : 0.f;
             const float f0 = w0 * inv, f1 = w1 * inv;
@@ -426,7 +427,7 @@ CISR_EXPORT int cisr_attn_prefill_tcgen05(const void* q, void* out, int n_tokens
                                           int n_pages, const int* req_slot, const int* block_table, int table_width,
                                           const int* tile_req, const int* tile_q0, int n_tiles, const int* q_start,
                                           const int* q_len, const int* ctx_len, int hq, int hkv, int page_size, float scale,
-                                          int window, int keep_first, float sink, void* stream) {
+                                          int window, int keep_first, float sink, const float* sink_heads, void* stream) {
     if (n_tiles <= 0) return 0;
     if (!g_encode || !g_error) return -13;
     if (hq % hkv || !cisr_attn_tcgen05_ok(page_size)) return -2;
@@ -448,5 +449,5 @@ CISR_EXPORT int cisr_attn_prefill_tcgen05(const void* q, void* out, int n_tokens
     }
     return launch_kernel(attn_prefill_tcgen05_kernel, dim3(n_tiles, hq), dim3(THREADS), smem, (cudaStream_t)stream, g_pdl, map_q,
                          map_k, map_v, (bf16*)out, (int)cache_rows, req_slot, block_table, table_width, tile_req, tile_q0,
-                         q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, keep_first, sink, g_error);
+                         q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, keep_first, sink, sink_heads, g_error);
 }

@@ -1,6 +1,7 @@
 // Row kernels of differential attention: two softmax maps per head over the same values, combined as
-//     o = a1 - lambda * a2,   o <- o / sqrt(mean(o^2) + eps) * out_scale,   o <- o * sigmoid(gate)
-// with q, k and v passing a short causal convolution over time right after their projection.
+//     o = a1 - lambda * a2,   o <- o / sqrt(mean(o^2) + eps) * out_scale,   o <- o * sigmoid(gate)   (the gate may be absent)
+// with q, k and v passing a short causal convolution over time right after their projection, or (no convolution) with the
+// leading coordinates of each map of q and k turned to the token's position.
 //
 // The two maps run on the engine's paged attention kernels as two query heads each (2 * heads query heads over kv_heads
 // key heads of one width D): a key row of the cache holds [k of map 1 | k of map 2 | zeros], a query row of map m holds
@@ -10,6 +11,8 @@
 //   diff_rows     per token: convolution of the q (, k, v) channels of the step's stacked projection (inputs before the
 //                 portion come from the request's kept inputs, zeros before the sequence), query rows in the layout
 //                 above, key and value rows into the request's cache pages.
+//   diff_rope_rows  the same rows without a convolution: each map's first 2 * rot_half coordinates of q and k turn by the
+//                 step's rotary tables (either pairing); values pass as they are.
 //   conv_keep     per request: the last taps - 1 convolution inputs become the request's kept inputs.
 //   diff_combine  per (token, head): the combination, the norm over the head's values and the gate, rounded once to the
 //                 operand type of the output projection.
@@ -289,11 +292,11 @@ diff_combine_kernel(const T* __restrict__ mixed, const float* __restrict__ gate,
     }
     sq = warp_sum(sq);
     const float inv = out_scale / sqrtf(sq / (float)dv + eps);
-    const float* g = gate + (size_t)t * row_stride + gate_col + h * dv;
+    const float* g = gate ? gate + (size_t)t * row_stride + gate_col + h * dv : nullptr;      // no gate: the factor is 1
     T* dst = out + ((size_t)t * hq + h) * dv;
     for (int d = lane; d < dv; d += 32) {
         const float o = to_float(a1[d]) - lambda * to_float(a2[d]);
-        dst[d] = from_float<T>(o * inv / (1.f + expf(-g[d])));
+        dst[d] = from_float<T>(g ? o * inv / (1.f + expf(-g[d])) : o * inv);
     }
 }
 
@@ -322,7 +325,7 @@ diff_combine_pairs_kernel(const T* __restrict__ mixed, const float* __restrict__
     const int t = pair / hq, h = pair - t * hq;
     const T* a1 = mixed + ((size_t)t * 2 * hq + 2 * h) * width;
     const T* a2 = a1 + width;
-    const float* g = gate + (size_t)t * row_stride + gate_col + h * dv;
+    const float* g = gate ? gate + (size_t)t * row_stride + gate_col + h * dv : nullptr;      // no gate: a logit of +inf, a factor of 1
     float2 o[kCombineKeep], gl[kCombineKeep];
     float sq = 0.f;
 #pragma unroll
@@ -331,7 +334,7 @@ diff_combine_pairs_kernel(const T* __restrict__ mixed, const float* __restrict__
         o[i] = make_float2(0.f, 0.f); gl[i] = o[i];
         if (d < dv) {
             const float2 x = Pair<T>::load(a1 + d), y = Pair<T>::load(a2 + d);
-            gl[i] = *reinterpret_cast<const float2*>(g + d);
+            gl[i] = g ? *reinterpret_cast<const float2*>(g + d) : make_float2(INFINITY, INFINITY);
             o[i] = make_float2(x.x - lambda * y.x, x.y - lambda * y.y);
             sq = fmaf(o[i].x, o[i].x, sq);
             sq = fmaf(o[i].y, o[i].y, sq);
@@ -346,7 +349,68 @@ diff_combine_pairs_kernel(const T* __restrict__ mixed, const float* __restrict__
         if (d < dv) store_pair<T>(dst + d, o[i].x * inv / (1.f + expf(-gl[i].x)), o[i].y * inv / (1.f + expf(-gl[i].y)));
     }
 }
+
+// Coordinate d of a map whose float coordinates are src[0 ..): turned by the token's tables when d < 2 * rot_half.
+__device__ __forceinline__ float turned(const float* __restrict__ src, int d, int rot_half, int interleaved,
+                                        const float* __restrict__ cs, const float* __restrict__ sn) {
+    if (d >= 2 * rot_half) return src[d];
+    int f, other; bool first;
+    if (interleaved) { f = d >> 1; first = !(d & 1); other = first ? d + 1 : d - 1; }
+    else { first = d < rot_half; f = first ? d : d - rot_half; other = first ? d + rot_half : d - rot_half; }
+    const float c = cs[f], s = sn[f], v = src[d], o = src[other];
+    return first ? v * c - o * s : v * c + o * s;
+}
+
+// A CTA per token.  proj [T, row_stride] float: q (hq x 2 x dk) from column 0, and where the layer has keys and values of
+// its own k (hkv x 2 x dk) from k_col and v (hkv x dv) from v_col.
+template <typename T>
+__global__ void __launch_bounds__(256)
+diff_rope_rows_kernel(const float* __restrict__ proj, int row_stride, int k_col, int v_col, const float* __restrict__ cos_t,
+                      const float* __restrict__ sin_t, int rot_half, int interleaved, const int* __restrict__ token_req,
+                      const int* __restrict__ req_slot, const int* __restrict__ positions, T* __restrict__ q_out, T* __restrict__ k_cache,
+                      T* __restrict__ v_cache, const int* __restrict__ block_table, int table_width, int page_size, int hq, int hkv,
+                      int dk, int dv, int width, int write_kv) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float* row = proj + (size_t)t * row_stride;
+    const float* cs = cos_t + (size_t)t * rot_half;
+    const float* sn = sin_t + (size_t)t * rot_half;
+    T* q_dst = q_out + (size_t)t * 2 * hq * width;
+    for (int i = threadIdx.x; i < 2 * hq * width; i += blockDim.x) {
+        const int r = i / width, col = i - r * width, m = r & 1, d = col - m * dk;      // row r: map m of head r / 2
+        q_dst[i] = from_float<T>(d >= 0 && d < dk ? turned(row + (size_t)r * dk, d, rot_half, interleaved, cs, sn) : 0.f);
+    }
+    if (!write_kv) return;
+    const int pos = positions[t];
+    const int page = block_table[(size_t)req_slot[token_req[t]] * table_width + pos / page_size];
+    if (page < 0) return;      // the host reserves a page before every write; never follow a missing entry
+    for (int i = threadIdx.x; i < hkv * width; i += blockDim.x) {
+        const int g = i / width, col = i - g * width;
+        const size_t at = (((size_t)page * hkv + g) * page_size + pos % page_size) * width + col;
+        float k = 0.f;
+        if (col < 2 * dk) { const int m = col / dk; k = turned(row + k_col + (size_t)(2 * g + m) * dk, col - m * dk, rot_half, interleaved, cs, sn); }
+        k_cache[at] = from_float<T>(k);
+        v_cache[at] = from_float<T>(col < dv ? row[v_col + g * dv + col] : 0.f);
+    }
+}
 }  // namespace
+
+CISR_EXPORT int cisr_diff_rope_rows(const float* proj, int row_stride, int k_col, int v_col, const float* cos_t, const float* sin_t,
+                                    int rot_half, int interleaved, const int* token_req, const int* req_slot, const int* positions,
+                                    void* q_out, void* k_cache, void* v_cache, int dtype, const int* block_table, int table_width,
+                                    int page_size, int tokens, int hq, int hkv, int dk, int dv, int width, int write_kv, void* stream) {
+    if (tokens <= 0) return 0;
+    if (width < 2 * dk || width < dv || 2 * rot_half > dk || rot_half < 0 || hq <= 0 || hkv <= 0) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CISR_BF16)
+        return launch_kernel(diff_rope_rows_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, s, g_pdl, proj, row_stride, k_col, v_col, cos_t,
+                             sin_t, rot_half, interleaved, token_req, req_slot, positions, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
+                             (__nv_bfloat16*)v_cache, block_table, table_width, page_size, hq, hkv, dk, dv, width, write_kv);
+    return launch_kernel(diff_rope_rows_kernel<float>, dim3(tokens), dim3(256), 0, s, g_pdl, proj, row_stride, k_col, v_col, cos_t, sin_t,
+                         rot_half, interleaved, token_req, req_slot, positions, (float*)q_out, (float*)k_cache, (float*)v_cache, block_table,
+                         table_width, page_size, hq, hkv, dk, dv, width, write_kv);
+}
 
 CISR_EXPORT int cisr_diff_rows(const float* proj, int row_stride, const float* conv_w, int taps, const float* state,
                                long long state_stride, const int* token_req, const int* req_slot, const int* q_start,

@@ -35,6 +35,7 @@ constexpr int BK = 64, UMMA_K = 16;     // BM = 128 (tcgen05.cuh)
 struct Epilogue {                       // what the epilogue variants need beyond the accumulator
     float* out_f32; bf16* out_bf16; int inter;
     float limit, alpha;                 // GATED: g' = min(g, limit), u' = clamp(u, +-limit), g' sigmoid(alpha g') (u' + 1)
+    int act;                            // RELU2's activation: 0 max(z, 0)^2, 1 the exact gelu z Phi(z)
     int accumulate;                     // PLAIN: out += product (the residual stream, in place) instead of out = product
     const float* cos_t; const float* sin_t; bf16* q_out; bf16* k_cache; bf16* v_cache; const int* positions;
     const int* token_req; const int* req_slot; const int* block_table; int table_width; int page_size; int hq; int hkv; int dim;
@@ -109,14 +110,18 @@ __device__ __forceinline__ void epilogue_tile(const Epilogue& ep, uint32_t lane_
             }
         }
     } else if (EPI == EPI_RELU2) {
-        // out = max(product, 0)^2 as bfloat16 [m, n]: the activation of an expert's first product
+        // out = act(product) as bfloat16 [m, n]: the activation of an expert's first product (max(z, 0)^2, or the exact gelu)
+        const bool gelu = ep.act == 1;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
             uint32_t v[32];
             tmem_load32(lane_base + (uint32_t)c, v);
             float act[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) { const float r = fmaxf(__uint_as_float(v[j]), 0.f); act[j] = r * r; }
+            for (int j = 0; j < 32; ++j) {
+                const float z = __uint_as_float(v[j]), r = fmaxf(z, 0.f);
+                act[j] = gelu ? 0.5f * z * (1.f + erff(z * 0.70710678118654752f)) : r * r;
+            }
             if (row < m && n0 + c < n) store_bf16x32(ep.out_bf16 + (size_t)row * n + n0 + c, act, n - (n0 + c));
         }
     } else if (EPI == EPI_GATED) {
@@ -482,7 +487,8 @@ CISR_EXPORT int cisr_gemm_tcgen05_rope(const void* a, const void* w, int m, int 
 
 // The product of rows sorted by group with each group's own weight matrix: a [m, k] with every group's rows padded to
 // whole 128-row tiles, w [groups * n, k] (group g's matrix in rows g * n ..), tile_group [m / 128] as described at
-// `Epilogue::tile_group`.  relu2 == 0: out is float [m, n] = a_g w_g^T; else out is bfloat16 [m, n] = max(a_g w_g^T, 0)^2.
+// `Epilogue::tile_group`.  relu2 == 0: out is float [m, n] = a_g w_g^T; 1: out is bfloat16 [m, n] = max(a_g w_g^T, 0)^2;
+// 2: out is bfloat16 [m, n] = gelu(a_g w_g^T), the exact gelu z Phi(z).
 CISR_EXPORT int cisr_gemm_tcgen05_grouped(const void* a, const void* w, void* out, int m, int n, int k, int groups,
                                           const int* tile_group, int relu2, void* stream) {
     if (m <= 0 || n <= 0) return 0;
@@ -494,6 +500,7 @@ CISR_EXPORT int cisr_gemm_tcgen05_grouped(const void* a, const void* w, void* ou
     const bool wide = wide_tiles(m, (n + 255) / 256);
     if (relu2) {
         ep.out_bf16 = (bf16*)out;
+        ep.act = relu2 == 2 ? 1 : 0;
         if (wide) return launch<256, 4, EPI_RELU2>(a, w, ep, m, n, k, (n + 255) / 256, s, groups);
         return launch<128, 3, EPI_RELU2>(a, w, ep, m, n, k, (n + 127) / 128, s, groups);
     }

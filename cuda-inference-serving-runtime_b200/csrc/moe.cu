@@ -6,8 +6,9 @@
 //   a choice bias (one number per router output, may be absent) is added to the scores for the choice only
 //   experts form n_groups equal groups of neighbours; a group's score is the sum of its two best members; only members
 //   of the `keep` best groups can be chosen (n_groups 0: all can)
-//   the `top` best open experts are chosen, weight = s * route_scale (not renormalised)
-//   y = sum over chosen e of weight_e * W_down_e act(W_up_e h),   act(z) = max(z, 0)^2, or the gated form
+//   the `top` best open experts are chosen, weight = s * route_scale; with `renormalize` the chosen scores are first
+//   divided by their sum (+ 1e-20)
+//   y = sum over chosen e of weight_e * W_down_e act(W_up_e h),   act(z) = max(z, 0)^2, the exact gelu z Phi(z), or the gated form
 //       act = g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit), where W_up_e stacks the
 //       gate rows on the up rows ([2 ff, hidden]) and alpha = 1.702
 //   router outputs beyond the experts that have matrices are identity experts: their output is the token's input h
@@ -66,7 +67,7 @@ __device__ __forceinline__ float warp_dot(const __nv_bfloat16* __restrict__ a, c
 constexpr int SELECT_WARPS = 4;
 __global__ void __launch_bounds__(32 * SELECT_WARPS)
 moe_select_kernel(const float* __restrict__ logits, int tokens, int n_experts, int top, int n_groups, int keep, float route_scale,
-                  int softmax, const float* __restrict__ choice_bias, int* __restrict__ chosen, float* __restrict__ weight) {
+                  int softmax, int renormalize, const float* __restrict__ choice_bias, int* __restrict__ chosen, float* __restrict__ weight) {
     extern __shared__ float select_smem[];
     pdl_trigger();
     pdl_wait();
@@ -133,6 +134,7 @@ moe_select_kernel(const float* __restrict__ logits, int tokens, int n_experts, i
             __syncwarp();
         }
     }
+    float chosen_sum = 0.f;                                          // lane 0's: the chosen scores, added best first
     for (int k = 0; k < top; ++k) {
         float v;
         int best = warp_best(rank, open_, n_experts, v);
@@ -141,14 +143,19 @@ moe_select_kernel(const float* __restrict__ logits, int tokens, int n_experts, i
             if (best == 0x7fffffff) best = 0;                        // fewer open experts than `top`: the host refuses such a configuration
             else open_[best] = 0;
             chosen[(size_t)t * top + k] = best;
-            weight[(size_t)t * top + k] = score[best] * route_scale;
+            chosen_sum += score[best];
+            weight[(size_t)t * top + k] = renormalize ? score[best] : score[best] * route_scale;
         }
         __syncwarp();
+    }
+    if (renormalize && lane == 0) {
+        const float den = chosen_sum + 1e-20f;
+        for (int k = 0; k < top; ++k) weight[(size_t)t * top + k] = weight[(size_t)t * top + k] / den * route_scale;
     }
 }
 
 CISR_EXPORT int cisr_moe_select(const float* logits, int tokens, int n_experts, int top, int n_groups, int keep, float route_scale,
-                                int softmax, const float* choice_bias, int* chosen, float* weight, void* stream) {
+                                int softmax, int renormalize, const float* choice_bias, int* chosen, float* weight, void* stream) {
     if (tokens <= 0) return 0;
     if (n_experts <= 0 || top <= 0 || top > n_experts || (n_groups > 0 && (n_experts % n_groups || keep <= 0 || keep > n_groups)))
         return -2;
@@ -156,19 +163,26 @@ CISR_EXPORT int cisr_moe_select(const float* logits, int tokens, int n_experts, 
     if (smem > 48 * 1024) return -3;
     return launch_kernel(moe_select_kernel, dim3((tokens + SELECT_WARPS - 1) / SELECT_WARPS), dim3(32 * SELECT_WARPS), smem,
                          (cudaStream_t)stream, g_pdl, logits, tokens, n_experts, top, n_groups > 0 ? n_groups : 0, keep, route_scale, softmax,
-                         choice_bias, chosen, weight);
+                         renormalize, choice_bias, chosen, weight);
 }
 
 // ---------------------------------------------------------------- few tokens: a warp per output feature
-// act[t * top + k, f] = max(W_up[e][f] . h[t], 0)^2 with e = chosen[t, k];   W_up [experts, ff, hidden].  gated: W_up
+// act[t * top + k, f] = a(W_up[e][f] . h[t]) with e = chosen[t, k] and a = max(z, 0)^2 (act 0) or the exact gelu (act 1);
+// W_up [experts, ff, hidden].  gated: W_up
 // [experts, 2 ff, hidden] (gate rows, then up rows) and act = g' sigmoid(alpha g') (u' + 1), g and u clamped by `limit`.
 // Pairs whose expert has no matrices (e >= n_real: an identity expert) are skipped.
 constexpr int ROW_WARPS = 8;
 constexpr float GATE_ALPHA = 1.702f;
+enum : int { ACT_RELU2 = 0, ACT_GELU_ERF = 1 };
+__device__ __forceinline__ float expert_act(float z, int act) {
+    if (act == ACT_GELU_ERF) return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+}
 template <typename T>
 __global__ void __launch_bounds__(32 * ROW_WARPS)
 moe_up_rows_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __restrict__ chosen, int hidden, int ff,
-                   int top, int n_real, int gated, float limit, T* __restrict__ act) {
+                   int top, int n_real, int gated, float limit, int act_kind, T* __restrict__ act) {
     pdl_trigger();
     pdl_wait();
     const int pair = blockIdx.x, lane = threadIdx.x & 31, f = blockIdx.y * ROW_WARPS + (threadIdx.x >> 5);
@@ -184,7 +198,7 @@ moe_up_rows_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const in
         return;
     }
     const float z = warp_dot(w_up + ((size_t)e * ff + f) * hidden, x, hidden, lane);
-    if (lane == 0) { const float r = fmaxf(z, 0.f); act[(size_t)pair * ff + f] = from_float<T>(r * r); }
+    if (lane == 0) act[(size_t)pair * ff + f] = from_float<T>(expert_act(z, act_kind));
 }
 
 // out[t, c] = out_scale[c] * sum_k weight[t, k] * (W_down[e_k][c] . act[t * top + k]);   W_down [experts, hidden, ff];
@@ -209,21 +223,21 @@ moe_down_rows_kernel(const T* __restrict__ act, const T* __restrict__ w_down, co
 
 CISR_EXPORT int cisr_moe_rows(const void* h, const void* w_up, const void* w_down, int dtype, const int* chosen,
                               const float* weight, int tokens, int hidden, int ff, int top, int n_real, int gated, float limit,
-                              void* act, const float* out_scale, float* out, void* stream) {
+                              int act_kind, void* act, const float* out_scale, float* out, void* stream) {
     if (tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 up_grid(tokens * top, (ff + ROW_WARPS - 1) / ROW_WARPS), down_grid(tokens, (hidden + ROW_WARPS - 1) / ROW_WARPS);
     int st;
     if (dtype == CISR_BF16) {
         st = launch_kernel(moe_up_rows_kernel<__nv_bfloat16>, up_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl, (const __nv_bfloat16*)h,
-                           (const __nv_bfloat16*)w_up, chosen, hidden, ff, top, n_real, gated, limit, (__nv_bfloat16*)act);
+                           (const __nv_bfloat16*)w_up, chosen, hidden, ff, top, n_real, gated, limit, act_kind, (__nv_bfloat16*)act);
         if (st) return st;
         return launch_kernel(moe_down_rows_kernel<__nv_bfloat16>, down_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl,
                              (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, chosen, weight, hidden, ff, top, n_real,
                              (const __nv_bfloat16*)h, out_scale, out);
     }
     st = launch_kernel(moe_up_rows_kernel<float>, up_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl, (const float*)h, (const float*)w_up,
-                       chosen, hidden, ff, top, n_real, gated, limit, (float*)act);
+                       chosen, hidden, ff, top, n_real, gated, limit, act_kind, (float*)act);
     if (st) return st;
     return launch_kernel(moe_down_rows_kernel<float>, down_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl, (const float*)act,
                          (const float*)w_down, chosen, weight, hidden, ff, top, n_real, (const float*)h, out_scale, out);

@@ -340,13 +340,20 @@ def attn_prefill_wide_ok(q: torch.Tensor, k_cache: torch.Tensor, page_size: int)
             and k_cache.shape[0] * k_cache.shape[1] * page_size < 2 ** 31)
 
 
-def _sink(sink: Optional[float]) -> ctypes.c_float:
-    """A softmax sink as the kernels take it: one more term exp(sink) in the denominator that carries no value; None: none."""
-    return ctypes.c_float(float("-inf") if sink is None else float(sink))
+def _sink(sink, hq: Optional[int] = None) -> tuple:
+    """A softmax sink as the kernels take it: one more term exp(sink) in the denominator that carries no value.  None:
+    none; a number: the same for every query head; a float tensor [hq]: one per query head.  Returns the two arguments
+    (the number, -inf where there is none; the per-head array or null)."""
+    if isinstance(sink, torch.Tensor):
+        _need(sink, torch.float32, "sink", 1)
+        if hq is not None and sink.numel() != hq:
+            raise KernelError("a per-head sink needs one number per query head")
+        return ctypes.c_float(float("-inf")), _p(sink)
+    return ctypes.c_float(float("-inf") if sink is None else float(sink)), _p(None)
 
 
 def attn_prefill_wide(q, out, k_cache, v_cache, req_slot, block_table, wide_req, wide_q0, q_start, q_len, ctx_len, hq, hkv,
-                      page_size, scale, window, sink: Optional[float] = None, keep_first: int = 0) -> None:
+                      page_size, scale, window, sink=None, keep_first: int = 0) -> None:
     """Attention of portions on tcgen05: q, out [tokens, hq, D]; tiles of 128 queries as (request, first query).
     `sink`: see `_sink`.  `keep_first`: the sequence's first keys that stay in sight behind a window."""
     dim = k_cache.shape[-1]
@@ -361,14 +368,14 @@ def attn_prefill_wide(q, out, k_cache, v_cache, req_slot, block_table, wide_req,
     _check(lib.cisr_attn_prefill_tcgen05(_p(q), _p(out), q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0], _p(req_slot),
                                          _p(block_table), block_table.shape[1], _p(wide_req), _p(wide_q0), wide_req.numel(),
                                          _p(q_start), _p(q_len), _p(ctx_len), hq, hkv, page_size, ctypes.c_float(scale),
-                                         int(window or 0), int(keep_first or 0), _sink(sink), _stream()), "attn_prefill_wide")
+                                         int(window or 0), int(keep_first or 0), *_sink(sink, hq), _stream()), "attn_prefill_wide")
 
 
 PREFILL_TILE = 64
 
 
 def attn_prefill(q, out, k_cache, v_cache, req_slot, block_table, tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv,
-                 page_size, scale, window, kind: str = "auto", sink: Optional[float] = None, keep_first: int = 0) -> None:
+                 page_size, scale, window, kind: str = "auto", sink=None, keep_first: int = 0) -> None:
     """Attention of portions: q, out [tokens, hq, D]; tiles list (request, first query of the tile).  Query i sees key
     j <= i when window is None or i - j < window or j < keep_first."""
     dim = k_cache.shape[-1]
@@ -380,13 +387,13 @@ def attn_prefill(q, out, k_cache, v_cache, req_slot, block_table, tile_req, tile
     lib = attention_library(dim, k_cache.dtype, kind)
     _check(lib.cisr_attn_prefill(_p(q), _p(out), _p(k_cache), _p(v_cache), _p(req_slot), _p(block_table), block_table.shape[1],
                                  _p(tile_req), _p(tile_q0), tile_req.numel(), _p(q_start), _p(q_len), _p(ctx_len),
-                                 hq, hkv, page_size, ctypes.c_float(scale), int(window or 0), int(keep_first or 0), _sink(sink),
+                                 hq, hkv, page_size, ctypes.c_float(scale), int(window or 0), int(keep_first or 0), *_sink(sink, hq),
                                  _stream()), "attn_prefill")
 
 
 def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec, q_start, ctx_len, partial, stats, hq, hkv,
                 page_size, scale, window, split_size, n_splits, kind: str = "auto", staging: str = "auto", merge: bool = True,
-                sink: Optional[float] = None, keep_first: int = 0) -> None:
+                sink=None, keep_first: int = 0) -> None:
     """Attention of single new tokens, split over key ranges of `split_size`, merged into out.  `keep_first`: the
     sequence's first keys that stay in sight behind a window.
 
@@ -412,7 +419,7 @@ def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec,
         raise KernelError("attn_decode: only the tensor-core kernels leave the merge to the caller")
     if sink is not None and not merge:
         raise KernelError("attn_decode: the sink is added by the merge kernel; a caller that merges itself cannot ask for one")
-    tail.append(_sink(sink))
+    tail.extend(_sink(sink, hq))
     tail.append(_stream())
     if staging not in ("auto", "tensor_map", "gather"):
         raise KernelError(f"unknown staging {staging!r}")
@@ -561,7 +568,7 @@ def _diff():
     lib = _diff_state.get("lib")
     if lib is None:
         lib = load_library("diff_attention.cu")
-        for name in ("cisr_diff_rows", "cisr_conv_keep", "cisr_diff_combine"):
+        for name in ("cisr_diff_rows", "cisr_diff_rope_rows", "cisr_conv_keep", "cisr_diff_combine"):
             getattr(lib, name).restype = ctypes.c_int
         lib.cisr_diff_set_pdl(int(_pdl_state["on"]))
         _diff_state["lib"] = lib
@@ -601,6 +608,36 @@ def diff_rows(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, state: torch.
                                   value_dim, width, int(write), _stream()), "diff_rows")
 
 
+def diff_rope_rows(proj: torch.Tensor, k_col: int, v_col: int, *, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot_half: int,
+                   interleaved: bool, token_req, req_slot, positions, q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+                   v_cache: Optional[torch.Tensor], block_table, page_size: int, hq: int, hkv: int, key_dim: int, value_dim: int) -> None:
+    """Per token of a step, without a convolution: the first 2 * rot_half coordinates of each map of q and k turn by the
+    step's rotary tables (cos, sin float [tokens, rot_half]; rot_half 0: nothing turns).  proj float [tokens, cols] holds q
+    [hq * 2 * key_dim] from column 0 and, when caches are given, k [hkv * 2 * key_dim] from `k_col` and v [hkv * value_dim]
+    from `v_col`.  Rows are laid out as `diff_rows` lays them out: query rows 2 h and 2 h + 1 of q_out [tokens, 2 hq, D],
+    a key row [k1 | k2 | 0] and a value row [v | 0] in the token's place in the pages [pages, hkv, page, D]."""
+    _need(proj, torch.float32, "proj", 2); _need(q_out, None, "q_out", 3)
+    tokens, width = q_out.shape[0], q_out.shape[2]
+    write = k_cache is not None
+    if rot_half:
+        _need(cos, torch.float32, "cos", 2); _need(sin, torch.float32, "sin", 2)
+        if cos.shape != (tokens, rot_half) or sin.shape != cos.shape:
+            raise KernelError("diff_rope_rows: rotary tables must be [tokens, rot_half]")
+    if (proj.shape[0] != tokens or q_out.shape[1] != 2 * hq or proj.shape[1] < hq * 2 * key_dim
+            or (write and (k_col + hkv * 2 * key_dim > proj.shape[1] or v_col + hkv * value_dim > proj.shape[1]))):
+        raise KernelError("diff_rope_rows: shapes disagree")
+    if write:
+        _need(k_cache, q_out.dtype, "k_cache", 4); _need(v_cache, q_out.dtype, "v_cache", 4)
+        if k_cache.shape[1:] != (hkv, page_size, width) or v_cache.shape != k_cache.shape:
+            raise KernelError("diff_rope_rows: the cache is not [pages, kv_heads, page, D]")
+    for name, t in (("token_req", token_req), ("req_slot", req_slot), ("positions", positions), ("block_table", block_table)):
+        _need(t, torch.int32, name)
+    _check(_diff().cisr_diff_rope_rows(_p(proj), proj.shape[1], k_col, v_col, _p(cos if rot_half else None), _p(sin if rot_half else None),
+                                       rot_half, int(interleaved), _p(token_req), _p(req_slot), _p(positions), _p(q_out), _p(k_cache),
+                                       _p(v_cache), dtype_code(q_out.dtype), _p(block_table), block_table.shape[1], page_size, tokens, hq,
+                                       hkv, key_dim, value_dim, width, int(write), _stream()), "diff_rope_rows")
+
+
 def conv_keep(proj: torch.Tensor, state: torch.Tensor, req_slot, q_start, q_len, n_req: int, taps: int, channels: int) -> None:
     """Per request of a step: the last taps - 1 rows of its portion's first `channels` columns of proj (older ones from
     what was kept before, where the portion is shorter) become its kept inputs, state [slots, taps - 1, channels]."""
@@ -611,16 +648,19 @@ def conv_keep(proj: torch.Tensor, state: torch.Tensor, req_slot, q_start, q_len,
                                   _p(q_len), n_req, taps, channels, _stream()), "conv_keep")
 
 
-def diff_combine(mixed: torch.Tensor, gate: torch.Tensor, gate_col: int, out: torch.Tensor, hq: int, value_dim: int, lam: float,
+def diff_combine(mixed: torch.Tensor, gate: Optional[torch.Tensor], gate_col: int, out: torch.Tensor, hq: int, value_dim: int, lam: float,
                  eps: float, out_scale: float) -> torch.Tensor:
     """Per (token, head): o = a1 - lam * a2 from rows 2 h and 2 h + 1 of mixed [tokens, 2 hq, D] (their first value_dim
     columns), o / sqrt(mean(o^2) + eps) * out_scale * sigmoid(gate), the gate's logits being columns gate_col + h *
-    value_dim of the float tensor `gate`; out [tokens, hq * value_dim] in mixed's type."""
-    _need(mixed, None, "mixed", 3); _need(gate, torch.float32, "gate", 2); _need(out, mixed.dtype, "out", 2)
+    value_dim of the float tensor `gate` (None: no gate); out [tokens, hq * value_dim] in mixed's type."""
+    _need(mixed, None, "mixed", 3); _need(out, mixed.dtype, "out", 2)
     tokens, _, width = mixed.shape
-    if mixed.shape[1] != 2 * hq or out.shape != (tokens, hq * value_dim) or gate.shape[0] != tokens or gate.shape[1] < gate_col + hq * value_dim:
+    if gate is not None:
+        _need(gate, torch.float32, "gate", 2)
+    if (mixed.shape[1] != 2 * hq or out.shape != (tokens, hq * value_dim)
+            or (gate is not None and (gate.shape[0] != tokens or gate.shape[1] < gate_col + hq * value_dim))):
         raise KernelError("diff_combine: shapes disagree")
-    _check(_diff().cisr_diff_combine(_p(mixed), _p(gate), gate.shape[1], gate_col, _p(out), dtype_code(mixed.dtype), tokens, hq, value_dim,
+    _check(_diff().cisr_diff_combine(_p(mixed), _p(gate), gate.shape[1] if gate is not None else 0, gate_col, _p(out), dtype_code(mixed.dtype), tokens, hq, value_dim,
                                      width, ctypes.c_float(lam), ctypes.c_float(eps), ctypes.c_float(out_scale), _stream()), "diff_combine")
     return out
 
@@ -895,6 +935,66 @@ def delta_step(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, state: torch
     return out
 
 
+# ------------------------------------------------------------------ lightning attention (linear attention with a fixed decay per head)
+_lightning_state = {}
+LIGHTNING_MAX_KEY_DIM = 256
+LIGHTNING_CHUNK = 64             # tokens per chunk of the chunked recurrence; portions of at least this many tokens run chunk by chunk
+
+
+def _lightning():
+    lib = _lightning_state.get("lib")
+    if lib is None:
+        lib = load_library("lightning.cu")
+        for name in ("cisr_lightning_recurrence", "cisr_lightning_output", "cisr_lightning_chunk_tokens", "cisr_lightning_max_key_dim"):
+            getattr(lib, name).restype = ctypes.c_int
+        assert lib.cisr_lightning_chunk_tokens() == LIGHTNING_CHUNK and lib.cisr_lightning_max_key_dim() == LIGHTNING_MAX_KEY_DIM
+        lib.cisr_lightning_set_pdl(int(_pdl_state["on"]))
+        _lightning_state["lib"] = lib
+    return lib
+
+
+def lightning_jobs():
+    return [("lightning.cu", {}, ())]
+
+
+def lightning_recurrence(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor,
+                         req_slot: torch.Tensor, q_start: torch.Tensor, q_len: torch.Tensor, n_req: int, o: torch.Tensor, heads: int,
+                         key_dim: int, value_dim: int, least: int = 0, n_long: int = 0, n_short: int = 0, columns_per_cta: int = 0) -> torch.Tensor:
+    """Per head S <- decay S + silu(k) silu(v)^T, o = S^T silu(q) over each request's tokens in order.  proj float
+    [tokens, columns] holds the projections' sums (q and k: heads x key_dim from `q_col` / `k_col`; v: heads x value_dim
+    from `v_col`); state float [slots, heads * value_dim * key_dim] is read and advanced; o float [tokens, heads *
+    value_dim].  `least` > 0: the `n_long` requests that bring at least that many tokens run chunk by chunk, the
+    `n_short` others token by token (the host knows the counts from the step's shape); 0: all token by token.
+    `columns_per_cta` (16, 32, 64; 0: by the size of the launch): value columns a CTA of the chunked form takes."""
+    _need(proj, torch.float32, "proj", 2); _need(decay, torch.float32, "decay", 1); _need(state, torch.float32, "state", 2)
+    _need(o, torch.float32, "o", 2)
+    for name, t in (("req_slot", req_slot), ("q_start", q_start), ("q_len", q_len)):
+        _need(t, torch.int32, name, 1)
+    tokens, cols = proj.shape
+    if (decay.numel() != heads or state.shape[1] != heads * key_dim * value_dim or o.shape != (tokens, heads * value_dim)
+            or max(q_col, k_col) + heads * key_dim > cols or v_col + heads * value_dim > cols or key_dim > LIGHTNING_MAX_KEY_DIM):
+        raise KernelError("lightning_recurrence: shapes disagree")
+    both = least > 0 and n_long > 0 and n_short > 0
+    _check(_lightning().cisr_lightning_recurrence(_p(proj), cols, q_col, k_col, v_col, _p(decay), _p(state), ctypes.c_longlong(state.shape[1]),
+                                                  _p(req_slot), _p(q_start), _p(q_len), _p(o), heads, key_dim, value_dim, n_req, int(least),
+                                                  int(n_long), int(n_short), int(columns_per_cta), _stream()), "lightning_recurrence",
+           own=2 if both else 1)
+    return o
+
+
+def lightning_output(o: torch.Tensor, gate: torch.Tensor, gate_col: int, norm_w: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out[:, :width] = o / sqrt(mean(o^2) + eps) * norm_w * sigmoid(gate[:, gate_col : gate_col + width]) with the mean over
+    a token's whole row (all heads at once); float arithmetic, rounded once to out's type.  out may be wider than o (padding
+    columns are left as they are)."""
+    _need(o, torch.float32, "o", 2); _need(gate, torch.float32, "gate", 2); _need(norm_w, torch.float32, "norm_w", 1); _need(out, None, "out", 2)
+    tokens, width = o.shape
+    if gate.shape[0] != tokens or gate_col + width > gate.shape[1] or norm_w.numel() != width or out.shape[0] != tokens or out.shape[1] < width:
+        raise KernelError("lightning_output: shapes disagree")
+    _check(_lightning().cisr_lightning_output(_p(o), _p(gate), gate.shape[1], gate_col, _p(norm_w), ctypes.c_float(eps), _p(out),
+                                              dtype_code(out.dtype), out.shape[1], width, tokens, _stream()), "lightning_output")
+    return out
+
+
 # ------------------------------------------------------------------ latent attention: the kernels around its products
 _latent_state = {}
 
@@ -1037,10 +1137,12 @@ def moe_jobs():
 
 
 def moe_select(logits: torch.Tensor, top: int, n_groups: int, keep: int, route_scale: float, chosen: torch.Tensor,
-               weight: torch.Tensor, scores: str = "sigmoid", choice_bias: Optional[torch.Tensor] = None) -> None:
+               weight: torch.Tensor, scores: str = "sigmoid", choice_bias: Optional[torch.Tensor] = None,
+               renormalize: bool = False) -> None:
     """Per token, from the router's logits (float [tokens, experts]): scores (`scores`: "sigmoid" of each logit, or
     "softmax" over all of them), the open groups, the `top` chosen experts (`chosen`, int32 [tokens, top], best first;
-    chosen by score + choice_bias where that is given) and their weights score * route_scale (`weight`, float)."""
+    chosen by score + choice_bias where that is given) and their weights score * route_scale (`weight`, float); with
+    `renormalize` the chosen scores are divided by their sum (+ 1e-20) before the scale."""
     _need(logits, torch.float32, "logits", 2); _need(chosen, torch.int32, "chosen", 2); _need(weight, torch.float32, "weight", 2)
     tokens, experts = logits.shape
     if chosen.shape != (tokens, top) or weight.shape != (tokens, top):
@@ -1052,7 +1154,7 @@ def moe_select(logits: torch.Tensor, top: int, n_groups: int, keep: int, route_s
         if choice_bias.numel() != experts:
             raise KernelError("moe_select: one choice bias per router output is needed")
     _check(_moe().cisr_moe_select(_p(logits), tokens, experts, top, n_groups, keep, ctypes.c_float(route_scale),
-                                  int(scores == "softmax"), _p(choice_bias), _p(chosen), _p(weight), _stream()), "moe_select")
+                                  int(scores == "softmax"), int(renormalize), _p(choice_bias), _p(chosen), _p(weight), _stream()), "moe_select")
 
 
 def _channel_scale(scale: Optional[torch.Tensor], hidden: int, what: str) -> None:
@@ -1063,8 +1165,10 @@ def _channel_scale(scale: Optional[torch.Tensor], hidden: int, what: str) -> Non
 
 
 def moe_rows(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
-             act: torch.Tensor, out: torch.Tensor, out_scale: Optional[torch.Tensor] = None, gate_limit: Optional[float] = None) -> torch.Tensor:
-    """out (float [tokens, hidden]) = sum over a token's chosen experts of weight * W_down_e relu(W_up_e h)^2, a warp per
+             act: torch.Tensor, out: torch.Tensor, out_scale: Optional[torch.Tensor] = None, gate_limit: Optional[float] = None,
+             activation: str = "relu_squared") -> torch.Tensor:
+    """out (float [tokens, hidden]) = sum over a token's chosen experts of weight * W_down_e a(W_up_e h) (`activation`:
+    "relu_squared" max(z, 0)^2 or "gelu" z Phi(z)), a warp per
     output feature; w_up [experts, ff, hidden], w_down [experts, hidden, ff]; `act` [tokens * top, ff] is scratch; `out_scale`
     (float, one per channel) multiplies the sum.  With `gate_limit` the experts are gated: w_up [experts, 2 ff, hidden]
     (gate rows, then up rows) and the activation is `gated_clamp`'s.  A chosen index beyond the experts that have
@@ -1081,11 +1185,14 @@ def moe_rows(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: 
         raise KernelError("moe_rows: shapes disagree")
     _channel_scale(out_scale, hidden, "moe_rows")
     _check(_moe().cisr_moe_rows(_p(h), _p(w_up), _p(w_down), dtype_code(h.dtype), _p(chosen), _p(weight), tokens, hidden, ff, top,
-                                experts, int(gate_limit is not None), ctypes.c_float(gate_limit or 0.0), _p(act), _p(out_scale), _p(out),
+                                experts, int(gate_limit is not None), ctypes.c_float(gate_limit or 0.0),
+                                0 if gate_limit is not None else EXPERT_ACTIVATIONS[activation],
+                                _p(act), _p(out_scale), _p(out),
                                 _stream()), "moe_rows", own=2)
     return out
 
 
+EXPERT_ACTIVATIONS = {"relu_squared": 0, "gelu": 1}      # ungated expert activations as the kernels number them
 MOE_TILE = 128                   # rows per tile of the grouped product: each expert's rows are padded to whole tiles
 MOE_GROUPED_MIN_ROWS = 64        # (token, expert) pairs per expert, on average, from which sorting and the grouped product pay
 
@@ -1147,7 +1254,8 @@ def moe_combine(sorted_out: torch.Tensor, row_of: torch.Tensor, weight: torch.Te
 
 
 def moe_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
-                out: torch.Tensor, out_scale: Optional[torch.Tensor] = None, gate_limit: Optional[float] = None) -> torch.Tensor:
+                out: torch.Tensor, out_scale: Optional[torch.Tensor] = None, gate_limit: Optional[float] = None,
+                activation: str = "relu_squared") -> torch.Tensor:
     """The same sum as `moe_rows` for many tokens: pairs sorted by expert on the device, activations gathered into that
     order, both products as grouped tcgen05 products (the activation, relu^2 or the clamped gated form over the stacked
     gate and up rows, as the first one's epilogue), rows summed per token with the router's weights in the router's
@@ -1168,7 +1276,8 @@ def moe_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chose
     moe_sort(chosen, experts, row_of, src_token, tile_group)
     sorted_h = moe_gather(h, src_token, torch.empty((rows, hidden), dtype=torch.bfloat16, device=device))
     if gate_limit is None:
-        act = gemm_tcgen05_grouped(sorted_h, w_up, torch.empty((rows, ff), dtype=torch.bfloat16, device=device), tile_group, tokens * top)
+        act = gemm_tcgen05_grouped(sorted_h, w_up, torch.empty((rows, ff), dtype=torch.bfloat16, device=device), tile_group, tokens * top,
+                                   activation=activation)
     else:
         act = gemm_tcgen05_grouped_gated(sorted_h, w_up, torch.empty((rows, ff), dtype=torch.bfloat16, device=device), tile_group,
                                          gate_limit, tokens * top)
@@ -1331,6 +1440,8 @@ def set_pdl(on: bool) -> None:
         _rows_state["lib"].cisr_attention_rows_set_pdl(int(on))
     if "lib" in _delta_state:
         _delta_state["lib"].cisr_delta_set_pdl(int(on))
+    if "lib" in _lightning_state:
+        _lightning_state["lib"].cisr_lightning_set_pdl(int(on))
     if "lib" in _diff_state:
         _diff_state["lib"].cisr_diff_set_pdl(int(on))
     if "lib" in _depth_state:
@@ -1520,17 +1631,19 @@ def gemm_tcgen05_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> 
 
 
 def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor,
-                         rows_in_use: Optional[int] = None) -> torch.Tensor:
+                         rows_in_use: Optional[int] = None, activation: str = "relu_squared") -> torch.Tensor:
     """Rows of `a` (bfloat16 [M, K], M a multiple of 128) sorted by group, each 128-row tile with its group's matrix
     w[g] (w bfloat16 [groups, N, K]; tile_group int32 [M / 128], -1: skip the tile).  out float [M, N]: the products;
-    out bfloat16 [M, N]: max(product, 0)^2.  `rows_in_use` (how many rows are not padding) only labels measurements."""
+    out bfloat16 [M, N]: the activation of the products (`activation`: "relu_squared" max(z, 0)^2, "gelu" z Phi(z)).
+    `rows_in_use` (how many rows are not padding) only labels measurements."""
     _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 3); _need(out, None, "out", 2); _need(tile_group, torch.int32, "tile_group", 1)
     m, k = a.shape
     groups, n, _ = w.shape
     if w.shape[2] != k or out.shape != (m, n) or m % 128 or tile_group.numel() != m // 128 or out.dtype not in (torch.float32, torch.bfloat16):
         raise KernelError(f"gemm grouped: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
     _check(_tcgen05().cisr_gemm_tcgen05_grouped(_p(a), _p(w), _p(out), m, n, k, groups, _p(tile_group),
-                                                int(out.dtype == torch.bfloat16), _stream()), "gemm_tcgen05_grouped")
+                                                1 + EXPERT_ACTIVATIONS[activation] if out.dtype == torch.bfloat16 else 0, _stream()),
+           "gemm_tcgen05_grouped")
     return out
 
 
@@ -1653,7 +1766,7 @@ _DESCRIBE = {
     "moe_sort": lambda chosen, experts, *a: (int(chosen.shape[0]), int(chosen.shape[1]), int(experts)),
     "moe_gather": lambda h, src_token, sorted_h: (int(sorted_h.shape[0]), int(sorted_h.shape[1])),
     "moe_combine": lambda sorted_out, row_of, weight, out, out_scale=None, h=None: (int(out.shape[0]), int(weight.shape[1]), int(out.shape[1])),
-    "gemm_tcgen05_grouped": lambda a, w, out, tile_group, rows_in_use=None:
+    "gemm_tcgen05_grouped": lambda a, w, out, tile_group, rows_in_use=None, activation="relu_squared":
         (int(rows_in_use or a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2]), out.dtype == torch.bfloat16),
     "gemm_tcgen05_grouped_gated": lambda a, w, out, tile_group, limit, rows_in_use=None:
         (int(rows_in_use or a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2])),
@@ -1677,6 +1790,11 @@ _DESCRIBE = {
     "diff_rows": lambda proj, conv_w, taps, state, **kw: (int(proj.shape[0]), int(conv_w.shape[1]), int(taps), int(kw["q_out"].shape[1] * kw["q_out"].shape[2]),
                                                          0 if kw.get("k_cache") is None else int(kw["k_cache"].shape[1] * kw["k_cache"].shape[3])),
     "conv_keep": lambda proj, state, req_slot, q_start, q_len, n_req, taps, channels: (int(n_req), int(channels), int(taps)),
+    "diff_rope_rows": lambda proj, k_col, v_col, **kw: (int(proj.shape[0]), int(proj.shape[1]), int(kw["q_out"].shape[1] * kw["q_out"].shape[2]),
+                                                        0 if kw.get("k_cache") is None else int(kw["k_cache"].shape[1] * kw["k_cache"].shape[3])),
+    "lightning_recurrence": lambda proj, q_col, k_col, v_col, decay, state, req_slot, q_start, q_len, n_req, o, heads, key_dim, value_dim, **kw:
+        (int(proj.shape[0]), int(n_req), int(heads), int(key_dim), int(value_dim), int(kw.get("n_long", 0))),
+    "lightning_output": lambda o, *a, **kw: (int(o.shape[0]), int(o.shape[1])),
     "diff_combine": lambda mixed, gate, gate_col, out, *a: (int(out.shape[0]), int(out.shape[1]), int(mixed.shape[1] * mixed.shape[2])),
     "depth_mix_norm": lambda hist, x, pending, w, n_new, **kw:
         (int(x.shape[0] if kw.get("rows") is None else kw["rows"].numel()), int(n_new), int(x.shape[1]), pending is not None,

@@ -85,6 +85,9 @@ class PendingNorm:
         self.delta = stream.pending
         self.delta_scale = getattr(stream, "pending_scale", None)
         self.resolved = False      # the norm has run (here or inside a product): stream.x is the sum, nothing is pending
+        # False where the arrangement multiplies the sub-block's output before it joins the stream: the part then hands its
+        # output back instead of adding it to `stream.x` in the epilogue of its last product
+        self.in_place_ok = True
 
     def fusable(self) -> bool:
         # a pending output that still has to be scaled per channel is added by the norm's own kernel

@@ -68,18 +68,24 @@ class PreNormBlock:
 
 
 class ChannelScale(Part):
-    """One factor per channel (a layer scale).  params: size; weight_name."""
+    """One factor per channel (a layer scale).  params: size; weight_name; value (optional: one constant for all channels,
+    a multiplier of the residual branch that the configuration gives; the part then has no tensor)."""
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
         self.size = int(spec["size"])
         self.weight_name = spec.get("weight_name", "")
+        self.value = spec.get("value")
         self.weight = None
 
     def tensor_needs(self):
-        return {self.weight_name: TensorNeed((self.size,), role="vector")}
+        return {} if self.value is not None else {self.weight_name: TensorNeed((self.size,), role="vector")}
 
     def load(self, tensors):
+        if self.value is not None:
+            from ..engine.model import require_cuda
+            self.weight = torch.full((self.size,), float(self.value), dtype=torch.float32, device=require_cuda())
+            return
         self.weight = tensors[self.weight_name].float().contiguous()    # applied to a float output on its way into the float stream
 
 
@@ -108,6 +114,7 @@ class PreNormScaledBlock:
 
     @staticmethod
     def _run(part, h, *args):
+        h.in_place_ok = False          # the output is scaled on its way into the stream: no part adds it there itself
         return part.forward(h if part.accepts_pending_norm else h.materialize(), *args)
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:

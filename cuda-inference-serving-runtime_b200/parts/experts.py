@@ -5,8 +5,10 @@
     bias      a per-output choice bias (`names["choice_bias"]`), added to s for the choice only; the weights use s
     groups    the experts form `groups` equal groups of neighbours; a group's score is the sum of its two best members;
               only members of the `keep` best groups can be chosen (groups 0: every expert can)
-    choice    the `top` best open experts, each weighted by s * route_scale (not renormalised)
-    expert    W_down act(W_up h), no biases; act(z) = max(z, 0)^2 ("relu_squared"); or gated ("gated_clamp"):
+    choice    the `top` best open experts, each weighted by s * route_scale; with `renormalize` the chosen scores are
+              divided by their sum (+ 1e-20) before the scale
+    expert    W_down act(W_up h), no biases; act(z) = max(z, 0)^2 ("relu_squared") or the exact gelu z Phi(z) ("gelu");
+              or gated ("gated_clamp"):
               g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), W_down (g sigmoid(1.702 g) (u + 1))
     identity  the last `identity` router outputs have no matrices: such an expert's output is h itself
     shared    an expert of the same form (its own width and limit) that every token uses, times sigmoid(w_sg . h)
@@ -25,7 +27,7 @@ from ..ops import kernels
 from .base import FEED_FORWARDS, FeedForward, TensorNeed, register
 from .linear import linear, linear_add
 
-ACTIVATIONS = ("relu_squared", "gated_clamp")
+ACTIVATIONS = ("relu_squared", "gelu", "gated_clamp")
 DEFAULT_NAMES = {"router": "router.weight", "up": "experts.{}.up.weight", "down": "experts.{}.down.weight",
                  "gate": "experts.{}.gate.weight", "choice_bias": "correction", "shared_gate": "shared.gate", "shared_up": "shared.up",
                  "shared_down": "shared.down", "shared_scale": "shared.sg"}
@@ -36,7 +38,7 @@ class RoutedExperts(FeedForward):
     """params: hidden_size, expert_size, experts, top, groups, keep, route_scale, activation, names (local tensor names:
     router, and up / down (/ gate) with {} for the expert's number); scores ("sigmoid" or "softmax"), choice_bias (bool),
     identity (router outputs beyond `experts` without matrices), limit (of the gated activation), shared (None, or
-    {"size", "limit"}: the shared expert)."""
+    {"size", "limit"}: the shared expert), renormalize (bool: the chosen scores are divided by their sum)."""
 
     applies_output_scale = True      # forward(h, ctx, out_scale): a per-channel layer scale is the epilogue of the last kernel
 
@@ -54,6 +56,7 @@ class RoutedExperts(FeedForward):
         self.scores = spec.get("scores", "sigmoid")
         self.has_choice_bias = bool(spec.get("choice_bias", False))
         self.identity = int(spec.get("identity") or 0)
+        self.renormalize = bool(spec.get("renormalize", False))
         self.gated = self.activation == "gated_clamp"
         self.limit = float(spec["limit"]) if self.gated else None
         shared = spec.get("shared")
@@ -120,7 +123,7 @@ class RoutedExperts(FeedForward):
         weight = torch.empty((tokens, self.top), dtype=torch.float32, device=h.device)
         logits = linear(h, self.router)          # float sums, by the engine's products for this many tokens
         kernels.moe_select(logits, self.top, self.groups, self.keep, self.route_scale, chosen, weight, scores=self.scores,
-                           choice_bias=self.choice_bias)
+                           choice_bias=self.choice_bias, renormalize=self.renormalize)
         return chosen, weight
 
     def shared_expert(self, h: torch.Tensor, into: torch.Tensor) -> torch.Tensor:
@@ -138,10 +141,12 @@ class RoutedExperts(FeedForward):
         if self.shared_size and out_scale is not None:
             raise NotImplementedError("a shared expert under a per-channel output scale is not built")
         if kernels.moe_grouped_ok(h, self.up, self.top, gated=self.gated):
-            kernels.moe_grouped(h, self.up, self.down, chosen, weight, out, out_scale, gate_limit=self.limit)   # many tokens: sorted by expert, tcgen05
+            kernels.moe_grouped(h, self.up, self.down, chosen, weight, out, out_scale, gate_limit=self.limit,
+                                activation=self.activation)                                         # many tokens: sorted by expert, tcgen05
         else:
             act = torch.empty((tokens * self.top, self.ff), dtype=self.dtype, device=h.device)
-            kernels.moe_rows(h, self.up, self.down, chosen, weight, act, out, out_scale, gate_limit=self.limit)
+            kernels.moe_rows(h, self.up, self.down, chosen, weight, act, out, out_scale, gate_limit=self.limit,
+                             activation=self.activation)
         if self.shared_size:
             self.shared_expert(h, out)
         return out

@@ -16,7 +16,7 @@ from .linear import as_tensor, linear, linear_to_stream, norm_fusable
 
 @register(FEED_FORWARDS, "swiglu")
 class SwiGLU(FeedForward):
-    """params: hidden_size, intermediate_size."""
+    """params: hidden_size, intermediate_size; names (local tensor names of gate, up, down)."""
 
     accepts_pending_norm = True
 
@@ -24,17 +24,18 @@ class SwiGLU(FeedForward):
         super().__init__(spec, dtype)
         self.hidden = int(spec["hidden_size"])
         self.inter = int(spec["intermediate_size"])
+        self.names = dict({"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}, **dict(spec.get("names") or {}))
         self.gate_up = None
         self.down = None
 
     def tensor_needs(self) -> Dict[str, TensorNeed]:
-        return {"gate_proj.weight": TensorNeed((self.inter, self.hidden)),
-                "up_proj.weight": TensorNeed((self.inter, self.hidden)),
-                "down_proj.weight": TensorNeed((self.hidden, self.inter))}
+        return {self.names["gate"]: TensorNeed((self.inter, self.hidden)),
+                self.names["up"]: TensorNeed((self.inter, self.hidden)),
+                self.names["down"]: TensorNeed((self.hidden, self.inter))}
 
     def load(self, tensors):
-        self.gate_up = torch.cat((tensors["gate_proj.weight"], tensors["up_proj.weight"]), dim=0).contiguous()
-        self.down = tensors["down_proj.weight"].contiguous()
+        self.gate_up = torch.cat((tensors[self.names["gate"]], tensors[self.names["up"]]), dim=0).contiguous()
+        self.down = tensors[self.names["down"]].contiguous()
 
     def kernel_jobs(self):
         return ([("elementwise.cu", {}, ())] + kernels.gemm_jobs(self.dtype)

@@ -7,8 +7,12 @@ Per token, with input h (the normed stream):
                  each head's q is [plain part (plain_dim) | rotated part (rot_dim)]
     latent       [c_raw | k_raw] = W_kvdown h;  c = unit(c_raw) * w_kvnorm (kv_rank wide);  k_rot = rotate(k_raw)
     per head     key_h = [W_kup_h c | k_rot],  value_h = W_vup_h c
-    scores       (q_h . key_h) * scale, causal softmax, out_h = sum of weights * value_h
+    scores       (q_h . key_h) * scale over the keys j <= i (with `window`: i - j < window), softmax (with `sink`: one more
+                 term exp(sink_h) per head in the denominator, with no key and no value), out_h = sum of weights * value_h
     output       W_out (concatenated heads [* sigmoid(W_gate h)])
+
+`shared_kv`: the layer has no down projection of its own and reads the cache rows of an earlier run entry (the run list's
+`cache_of`) as they are stored, with its own up projections, queries, window and sink.
 
 unit(v) = v / sqrt(mean(v^2) + eps).  The cache row of a token is [c | k_rot | 0 pad]: one plane, one "head".  Since
 q_h,plain . (W_kup_h c) = (W_kup_h^T q_h,plain) . c, each query is carried into the latent's basis once
@@ -33,7 +37,7 @@ from .base import MIXERS, POSITIONS, Mixer, TensorNeed, build_part, register
 from .linear import as_tensor, linear, norm_fusable
 
 ROW_STEP = 16          # cache rows are padded to a multiple of this (the attention kernels' head sizes)
-DEFAULT_NAMES = {"q": "q_proj.weight", "q_down": "q_down.weight", "q_norm": "q_norm.weight", "q_up": "q_up.weight",
+DEFAULT_NAMES = {"sink": "sink", "q": "q_proj.weight", "q_down": "q_down.weight", "q_norm": "q_norm.weight", "q_up": "q_up.weight",
                  "kv_down": "kv_down.weight", "kv_norm": "kv_norm.weight", "k_up": "k_up.weight", "v_up": "v_up.weight",
                  "gate": "gate.weight", "out": "o_proj.weight"}
 
@@ -42,7 +46,9 @@ DEFAULT_NAMES = {"q": "q_proj.weight", "q_down": "q_down.weight", "q_norm": "q_n
 class LatentAttention(Mixer):
     """params: hidden_size, num_heads, plain_dim, rot_dim, value_dim, kv_rank, q_rank (0: queries straight from the
     input), gate (bool: sigmoid output gate), position (PartSpec of a rotary encoding over rot_dim), scale, eps,
-    names (local tensor names of q, q_down, q_norm, q_up, kv_down, kv_norm, k_up, v_up, gate, out)."""
+    window (None or int: the keys a query keeps in sight), sink (bool: a learned softmax sink per head), shared_kv (bool:
+    no down projection, the cache rows of another run entry), names (local tensor names of q, q_down, q_norm, q_up,
+    kv_down, kv_norm, k_up, v_up, gate, out, sink)."""
 
     graph_safe = True
     accepts_pending_norm = True
@@ -59,6 +65,10 @@ class LatentAttention(Mixer):
         self.gate = bool(spec.get("gate", False))
         self.scale = float(spec["scale"])
         self.eps = float(spec["eps"])
+        self.window = spec.get("window")
+        self.has_sink = bool(spec.get("sink", False))
+        self.shared_kv = bool(spec.get("shared_kv", False))
+        self.sink = None
         self.names = {**DEFAULT_NAMES, **dict(spec.get("names") or {})}
         self.position = build_part(POSITIONS, spec["position"], dtype, "position encoding")
         if self.rot % 2 or getattr(self.position, "dim", self.rot) != self.rot:
@@ -71,11 +81,14 @@ class LatentAttention(Mixer):
     # ---------------------------------------------------------------- tensors
     def tensor_needs(self) -> Dict[str, TensorNeed]:
         n, H = self.names, self.heads
-        needs = {n["kv_down"]: TensorNeed((self.kv_rank + self.rot, self.hidden)),
-                 n["kv_norm"]: TensorNeed((self.kv_rank,), role="vector"),
-                 n["k_up"]: TensorNeed((H * self.plain, self.kv_rank)),
+        needs = {n["k_up"]: TensorNeed((H * self.plain, self.kv_rank)),
                  n["v_up"]: TensorNeed((H * self.vdim, self.kv_rank)),
                  n["out"]: TensorNeed((self.hidden, H * self.vdim))}
+        if not self.shared_kv:
+            needs[n["kv_down"]] = TensorNeed((self.kv_rank + self.rot, self.hidden))
+            needs[n["kv_norm"]] = TensorNeed((self.kv_rank,), role="vector")
+        if self.has_sink:
+            needs[n["sink"]] = TensorNeed((H,), role="vector", init_mean=0.0, init_std=1.0)
         if self.q_rank:
             needs[n["q_down"]] = TensorNeed((self.q_rank, self.hidden))
             needs[n["q_norm"]] = TensorNeed((self.q_rank,), role="vector")
@@ -90,13 +103,14 @@ class LatentAttention(Mixer):
         n, H = self.names, self.heads
         # one product serves every projection that reads the layer's input: [queries or their latent | kv latent + key part | gate]
         first = tensors[n["q_down"]] if self.q_rank else tensors[n["q"]]
-        stacked = [first, tensors[n["kv_down"]]] + ([tensors[n["gate"]]] if self.gate else [])
+        stacked = [first] + ([] if self.shared_kv else [tensors[n["kv_down"]]]) + ([tensors[n["gate"]]] if self.gate else [])
         self.w_in = torch.cat(stacked, dim=0).contiguous()
         self.c_col = first.shape[0]
-        self.gate_col = self.c_col + self.kv_rank + self.rot
+        self.gate_col = self.c_col + (0 if self.shared_kv else self.kv_rank + self.rot)
         self.q_up = tensors[n["q_up"]].contiguous() if self.q_rank else None
         self.q_norm = tensors[n["q_norm"]].float().contiguous() if self.q_rank else None
-        self.kv_norm = tensors[n["kv_norm"]].float().contiguous()
+        self.kv_norm = None if self.shared_kv else tensors[n["kv_norm"]].float().contiguous()
+        self.sink = tensors[n["sink"]].float().contiguous() if self.has_sink else None      # a score: float whatever the storage type
         self.k_up = tensors[n["k_up"]].contiguous().view(H, self.plain, self.kv_rank)     # per head [plain_dim (k), kv_rank (n)]
         self.v_up = tensors[n["v_up"]].contiguous().view(H, self.vdim, self.kv_rank)      # per head [value_dim (n), kv_rank (k)]
         self.o = tensors[n["out"]].contiguous()
@@ -107,7 +121,7 @@ class LatentAttention(Mixer):
                 + (kernels.skinny_jobs() if self.dtype == torch.bfloat16 else []))
 
     def cache_use(self) -> CacheUse:
-        return CacheUse("pages", kv_heads=1, head_dim=self.row, window=None, planes=1)
+        return CacheUse("pages", kv_heads=1, head_dim=self.row, window=self.window, planes=1)
 
     # ---------------------------------------------------------------- the step
     def plan_key(self):
@@ -120,6 +134,8 @@ class LatentAttention(Mixer):
         self.position.rotation(ctx)
 
     def forward(self, h, ctx, cache):
+        if cache.write == self.shared_kv:
+            raise ValueError("latent_attention: a layer with a down projection writes its own cache rows, one without reads another entry's")
         tokens, H, device = ctx.n_tokens, self.heads, ctx.device
         rot = self.position.rotation(ctx)
         table = dict(cos=rot.cos, sin=rot.sin, rot_half=rot.rot_half, interleaved=rot.interleaved)
@@ -133,9 +149,10 @@ class LatentAttention(Mixer):
         else:
             proj = linear(as_tensor(h), self.w_in)                             # float [tokens, stacked rows]
         cq = torch.empty((tokens, self.q_rank), dtype=self.dtype, device=device) if self.q_rank else None
-        kernels.latent_rows(proj, 0, self.q_rank, self.q_norm, cq, self.c_col, self.kv_rank, self.kv_norm, self.eps,
-                            cache=cache.k if cache.write else None, token_req=ctx.token_req, positions=ctx.positions,
-                            req_slot=ctx.req_slot, block_table=cache.block_table, page_size=cache.page_size, **table)
+        if self.q_rank or cache.write:
+            kernels.latent_rows(proj, 0, self.q_rank, self.q_norm, cq, self.c_col, self.kv_rank, self.kv_norm, self.eps,
+                                cache=cache.k if cache.write else None, token_req=ctx.token_req, positions=ctx.positions,
+                                req_slot=ctx.req_slot, block_table=cache.block_table, page_size=cache.page_size, **table)
         q = linear(cq, self.q_up) if self.q_rank else proj                     # heads of [plain | rotated part] from column 0
         q_rows = torch.empty((tokens, H, self.row), dtype=self.dtype, device=device)
         few = tokens <= kernels.LATENT_ROW_KERNEL_MAX_TOKENS
@@ -145,7 +162,7 @@ class LatentAttention(Mixer):
             q_plain = torch.empty((tokens, H, self.plain), dtype=self.dtype, device=device)
             kernels.latent_query(q, 0, H, self.plain, plain_out=q_plain, q_rows=q_rows, kv_rank=self.kv_rank, **table)
             kernels.gemm_heads(q_plain, self.k_up, q_rows, w_is_nk=False)      # q_rows[:, h, :kv_rank] = W_kup_h^T q_plain_h
-        mixed = paged_attention(ctx.plan_for(self), q_rows, cache.k, cache.k, cache, ctx, H, 1, self.scale, None)
+        mixed = paged_attention(ctx.plan_for(self), q_rows, cache.k, cache.k, cache, ctx, H, 1, self.scale, self.window, sink=self.sink)
         if few:      # W_vup_h (weighted sum of latents), gate and rounding in one row kernel
             values = kernels.latent_values(mixed, self.v_up, proj if self.gate else None, self.gate_col,
                                            torch.empty((tokens, H * self.vdim), dtype=self.dtype, device=device))

@@ -58,7 +58,7 @@ def stream_target(h, tokens: int, width: int):
     `PendingNorm` that is resolved by now (the norm has run, here or inside a product, so `h.stream.x` holds x + the
     output before and nothing is pending), float, contiguous and [tokens, width].  Otherwise None."""
     from .base import PendingNorm
-    if not (isinstance(h, PendingNorm) and h.resolved and h.stream.pending is None):
+    if not (isinstance(h, PendingNorm) and h.resolved and h.in_place_ok and h.stream.pending is None):
         return None
     x = h.stream.x
     if x.dtype != torch.float32 or x.shape != (tokens, width) or not x.is_contiguous():

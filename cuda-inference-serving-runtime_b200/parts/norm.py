@@ -56,6 +56,16 @@ class ScalarRMSNorm(RMSNorm):
         self.weight = tensors[self.weight_name].float().reshape(1).expand(self.size).contiguous()
 
 
+@register(NORMS, "rms_norm_offset")
+class OffsetRMSNorm(RMSNorm):
+    """x / sqrt(mean(x^2) + eps) * (1 + w): the weight is stored around zero.  params: size, eps; weight_name.  1 + w is
+    formed once at load, in float (it has no exact bfloat16 form), so every kernel that takes RMSNorm takes this one as
+    it is: their weights may be float whatever the storage type."""
+
+    def load(self, tensors):
+        self.weight = (1.0 + tensors[self.weight_name].float()).contiguous()
+
+
 @register(NORMS, "layer_norm")
 class LayerNorm(Norm):
     """(x - mean) / sqrt(var + eps) * w over the channels, var the mean squared deviation, no bias.

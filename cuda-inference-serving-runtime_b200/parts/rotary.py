@@ -68,6 +68,8 @@ def scaled_frequencies(freq: torch.Tensor, theta: float, dim: int, scaling) -> t
     import math
 
     kind = scaling.get("kind", "yarn")
+    if kind == "wavelength":
+        return frequencies_by_wavelength(freq, scaling), 1.0
     if kind != "yarn":
         raise ValueError(f"unknown rotary scaling {kind!r}")
     factor, original = float(scaling["factor"]), float(scaling["original"])
@@ -80,6 +82,20 @@ def scaled_frequencies(freq: torch.Tensor, theta: float, dim: int, scaling) -> t
     index = torch.arange(freq.numel(), dtype=torch.float64)
     ramp = ((index - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
     return freq / factor * ramp + freq * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+def frequencies_by_wavelength(freq: torch.Tensor, scaling) -> torch.Tensor:
+    """kind "wavelength" (factor, low, high, original): a pair is judged by its wavelength l = 2 pi / f against the
+    original length.  Waves shorter than original / high keep their frequency, waves longer than original / low are slowed
+    by `factor`, and between the two the frequency is blended by s = (original / l - low) / (high - low):
+    f' = (1 - s) f / factor + s f.  The tables' magnitude stays 1."""
+    import math
+
+    factor, low, high, original = (float(scaling[key]) for key in ("factor", "low", "high", "original"))
+    wave = 2.0 * math.pi / freq
+    blend = (original / wave - low) / (high - low)
+    mixed = (1.0 - blend) * freq / factor + blend * freq
+    return torch.where(wave < original / high, freq, torch.where(wave > original / low, freq / factor, mixed))
 
 
 @register(POSITIONS, "rotary_interleaved")
