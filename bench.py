@@ -27,9 +27,11 @@ every request holding about 4096 tokens of context while it decodes.  Prints ONE
 --workload mixed: the continuous-batching workload (by default the SmolLM2-1.7B sizes, 64 requests with prompts
 of 128 to 2048 tokens, 256 generated tokens each) through the scheduler with graphs on; prints total, prefill
 and decode tokens per second, launch counts, graph statistics and a roofline for the whole run.
---designs SIZES [--design zurolorn|ronolorn|gipozen]: Zurolorn (latent attention, routed experts), Ronolorn (windowed attention,
-gated delta rule, several residual streams) or Gipozen (differential attention with convolved projections, depth-weighted
-average of the stream, PolyNorm and routed gated feed-forwards) beside the Llama shape of equal size at the named widths:
+--designs SIZES [--design zurolorn|ronolorn|gipozen|vilodra]: Zurolorn (latent attention, routed experts), Ronolorn (windowed
+attention, gated delta rule, several residual streams), Gipozen (differential attention with convolved projections,
+depth-weighted average of the stream, PolyNorm and routed gated feed-forwards) or Vilodra (lightning attention with a state
+per head, differential attention with rotary positions, windowed latent attention with sinks, gelu experts) beside the
+Llama shape of equal size at the named widths:
 prompt and decode tokens per second of both, and per kind of kernel the device time and the distance from the roofline.
 --impl reference: the reference's own stock code on the same decode workload (see reference_arm).
 
@@ -486,6 +488,35 @@ def gipozen_pair(width: int, layers: int, heads: int, ff_active: int, experts: i
     return gipo, design_pair(width, layers, heads, ff_active, experts, top, vocab)[1]
 
 
+def vilodra_pair(width: int, layers: int, heads: int, ff_active: int, experts: int = 0, top: int = 0, vocab: int = 32000):
+    """A Vilodra shape and the Llama shape of equal size beside it: the same width, layers and vocabulary (the table is also
+    the head).  Layers in the order lightning, latent attention, differential attention, latent attention that reads the
+    second layer's cache rows; lightning heads of 128 (half as many as Llama's heads of 64), two maps of 32 per query head
+    with values of 64 and a quarter as many key heads, latent rows of 96 + 32 behind windows of 1024 keys; dense gated
+    feed-forwards on even layers, `top` of `experts` gelu experts (together as wide as the dense one) on odd ones."""
+    experts, top = max(experts, 4), max(top, 1)
+    lh = max(1, heads // 2)
+    light = {"heads": lh, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(5.0 + 3.0 * h / lh) for h in range(lh)]}
+    yarn = {"base": 10000.0, "dims": 32, "scaling": {"factor": 4.0, "original": 2048, "fast": 16.0, "slow": 2.0}}
+    lat = {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 96, "rot": yarn, "scale": 96 ** -0.5, "mask": {"size": 1024}}
+    diff = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 32, "vdim": 64, "scale": 32 ** -0.5, "diff": 0.6,
+            "rot": {"base": 10000.0, "dims": 32, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+    dense = {"kind": "dense", "ff": ff_active}
+    moe = {"kind": "moe", "expert": {"ff": ff_active // top}, "router": {"experts": experts, "top": top, "scale": 1.0}}
+
+    def layer(i):
+        kind = i % 4
+        if kind == 0:
+            return {"type": "lightning", "mixer": light, "mlp": dense}
+        if kind == 2:
+            return {"type": "attention", "mixer": diff, "mlp": dense}
+        return {"type": "latent_attention", "mixer": lat if kind == 1 else dict(lat, kv_from=i - 2), "mlp": moe}
+
+    vilo = {"architecture": "Vilodra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.7, "max_positions": 8192,
+            "layers": [layer(i) for i in range(layers)]}
+    return vilo, design_pair(width, layers, heads, ff_active, experts, top, vocab)[1]
+
+
 DESIGN_SIZES = {"1024": (1024, 8, 16, 2048, 16, 4), "2048": (2048, 8, 32, 4096, 32, 4), "4096": (4096, 4, 32, 8192, 64, 8)}
 KERNEL_KIND = {   # which kernels of the two designs are alike
     "gemm_tcgen05": "product, many tokens", "gemm_library": "product, many tokens", "gemm_tcgen05_swiglu": "feed-forward product, many tokens",
@@ -499,7 +530,7 @@ KERNEL_KIND = {   # which kernels of the two designs are alike
     "hyper_mix_norm": "norm", "attention_rows": "row kernels", "activation": "row kernels", "delta_prepare": "row kernels",
     "delta_output": "row kernels", "delta_keep": "bookkeeping", "delta_recurrence": "recurrence", "delta_chunks": "recurrence",
     "diff_rows": "row kernels", "diff_combine": "row kernels", "conv_keep": "bookkeeping", "depth_mix_norm": "norm", "polynorm": "row kernels",
-    "gated_clamp": "row kernels"}
+    "gated_clamp": "row kernels", "lightning_recurrence": "recurrence", "lightning_output": "row kernels", "diff_rope_rows": "row kernels"}
 
 
 def generic_need(name: str, shape: tuple, cache_tokens: int, causal: int):
@@ -563,6 +594,16 @@ def generic_need(name: str, shape: tuple, cache_tokens: int, causal: int):
         # (seven operations per state element and token), which the tensor-core peak does not describe: bytes only
         tokens, n_req, heads, kvh, dk, dv = shape
         return (n_req * 2 * heads * dk * dv + tokens * (2 * kvh * dk + 2 * heads * dv + 2 * heads)) * 4, 0.0
+    if name == "lightning_recurrence":
+        # the state once in and once out per request, the tokens' projections once in, the read-outs once out; the arithmetic is
+        # float on the CUDA cores (about four operations per state element and token), which the tensor-core peak does not describe
+        tokens, n_req, heads, dk, dv, n_long = shape
+        return (n_req * 2 * heads * dk * dv + tokens * heads * (2 * dk + 2 * dv)) * 4, 0.0
+    if name == "lightning_output":
+        return shape[0] * shape[1] * 10, 0.0
+    if name == "diff_rope_rows":
+        tokens, cols, q_cols, kv_cols = shape
+        return tokens * (cols * 4 + (q_cols + 2 * kv_cols) * 2), 0.0
     if name == "diff_rows":
         tokens, channels, taps, q_cols, kv_cols = shape
         return tokens * (channels * 4 + (q_cols + 2 * kv_cols) * 2), 2.0 * tokens * channels * taps
@@ -656,7 +697,7 @@ def design_comparison(args, hbm_gbs: float, burst_tflops: float, peak_source: st
 
     sizes = [s for s in args.designs.split(",") if s]
     batch, context, prompt = args.batch, min(args.context, 2048), PREFILL_TOKENS
-    pair = {"ronolorn": ronolorn_pair, "gipozen": gipozen_pair}.get(args.design, design_pair)
+    pair = {"ronolorn": ronolorn_pair, "gipozen": gipozen_pair, "vilodra": vilodra_pair}.get(args.design, design_pair)
     line = {"designs": f"{args.design} beside llama at equal size", "dtype": "bf16", "data": "synthetic token ids, seeded random weights",
             "batch": batch, "context": context, "prompt_tokens": prompt, "peaks": peak_source, "sizes": {}}
     sampler = ClockSampler().start()
@@ -919,10 +960,11 @@ def main() -> int:
     parser.add_argument("--designs", metavar="SIZES", default=None,
                         help="instead of the default workload: Zurolorn beside the Llama shape of equal size, prompt and decode, at "
                              "the named widths (comma-separated, from 1024, 2048, 4096)")
-    parser.add_argument("--design", choices=["zurolorn", "ronolorn", "gipozen"], default="zurolorn",
+    parser.add_argument("--design", choices=["zurolorn", "ronolorn", "gipozen", "vilodra"], default="zurolorn",
                         help="--designs: which design stands beside the Llama shape (ronolorn: windowed attention, gated delta rule, "
                              "four residual streams, dense feed-forward; gipozen: differential attention, depth-weighted average, "
-                             "PolyNorm and routed gated feed-forwards)")
+                             "PolyNorm and routed gated feed-forwards; vilodra: lightning attention, differential attention with "
+                             "rotary positions, windowed latent attention with sinks, dense gated and routed gelu feed-forwards)")
     args = parser.parse_args()
     if args.workload == "mixed" and "--preset" not in " ".join(sys.argv):
         args.preset = "smollm2-1.7b"

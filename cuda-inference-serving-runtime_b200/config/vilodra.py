@@ -7,8 +7,8 @@ config.json of this design, key by key:
 
     architecture        "Vilodra"
     vocab, width        sizes of the token table and of the residual stream
-    norm.eps            eps of every RMS norm (the layers' and the final norm, whose weights are stored around zero and
-                        applied as 1 + w; the lightning mixer's output norm; the latent's norm; the per-head norm of the
+    norm.eps            eps of every RMS norm (the layers' and the final norm, whose weights are offsets from one: the factor is
+                        1 + w; the lightning mixer's output norm; the latent's norm; the per-head norm of the
                         differential attention)
     residual_mult       x <- x + residual_mult * f(norm(x)) for the mixer and for the feed-forward
     layers[i]           type, mixer, mlp:
@@ -100,7 +100,7 @@ class VilodraConfig:
         return PartSpec("diff_attention", {
             "hidden_size": width, "num_heads": heads, "num_kv_heads": kv_heads, "key_dim": dim, "value_dim": vdim,
             "scale": float(_need(m, "scale", at)), "diff": float(_need(m, "diff", at)), "eps": eps, "conv": 0, "gate": False,
-            "position": position, "window": None, "keep_first": 0, "shared_kv": False})
+            "position": position, "window": None, "keep_first": 0, "shared_kv": False, "in_place": True})
 
     @staticmethod
     def _latent(layers, i: int, at: str, width: int, eps: float) -> PartSpec:

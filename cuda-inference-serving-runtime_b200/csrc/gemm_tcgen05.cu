@@ -36,7 +36,8 @@ struct Epilogue {                       // what the epilogue variants need beyon
     float* out_f32; bf16* out_bf16; int inter;
     float limit, alpha;                 // GATED: g' = min(g, limit), u' = clamp(u, +-limit), g' sigmoid(alpha g') (u' + 1)
     int act;                            // RELU2's activation: 0 max(z, 0)^2, 1 the exact gelu z Phi(z)
-    int accumulate;                     // PLAIN: out += product (the residual stream, in place) instead of out = product
+    int accumulate;                     // PLAIN: out += product
+    float out_mult;                     // PLAIN: the product is multiplied by it first (a constant factor of the residual branch); 0: no factor (the residual stream, in place) instead of out = product
     const float* cos_t; const float* sin_t; bf16* q_out; bf16* k_cache; bf16* v_cache; const int* positions;
     const int* token_req; const int* req_slot; const int* block_table; int table_width; int page_size; int hq; int hkv; int dim;
     // Grouped product: the rows of `a` are sorted by group (an expert), each group's rows padded to whole 128-row tiles;
@@ -85,6 +86,10 @@ __device__ __forceinline__ void epilogue_tile(const Epilogue& ep, uint32_t lane_
         for (int c = 0; c < BN; c += 32) {
             uint32_t v[32];
             tmem_load32(lane_base + (uint32_t)c, v);
+            if (ep.out_mult != 0.f) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * ep.out_mult);
+            }
             if (row < m) {
                 float* dst = ep.out_f32 + (size_t)row * n + n0 + c;
                 if (n0 + c + 32 <= n && (n & 3) == 0) {
@@ -423,13 +428,15 @@ CISR_EXPORT void cisr_gemm_tcgen05_set_map_cache_limit(int entries) { g_map_cach
 // Three pipeline stages keep a CTA near 100 KB of shared memory, so two CTAs share an SM and one's epilogue overlaps
 // the other's main loop.
 // accumulate != 0: out += a w^T (each output element is read, added to in float and written by the one thread that
-// owns it: what the residual add of a layer does, without a pass of its own).
-CISR_EXPORT int cisr_gemm_tcgen05(const void* a, const void* w, float* out, int m, int n, int k, int accumulate, void* stream) {
+// owns it: what the residual add of a layer does, without a pass of its own).  out_mult: the product is multiplied by it
+// before it is written or added (1: as it is).
+CISR_EXPORT int cisr_gemm_tcgen05(const void* a, const void* w, float* out, int m, int n, int k, int accumulate, float out_mult,
+                                  void* stream) {
     if (m <= 0 || n <= 0) return 0;
     if (!g_encode || !g_error) return -13;
     if (!operands_ok(a, w, k) || ((uintptr_t)out & 15)) return -2;
     Epilogue ep = {};
-    ep.out_f32 = out; ep.accumulate = accumulate != 0;
+    ep.out_f32 = out; ep.accumulate = accumulate != 0; ep.out_mult = out_mult == 1.f ? 0.f : out_mult;
     cudaStream_t s = (cudaStream_t)stream;
     if (n <= 64) return launch<64, 8, EPI_PLAIN>(a, w, ep, m, n, k, (n + 63) / 64, s);
     if (wide_tiles(m, (n + 255) / 256)) return launch<256, 4, EPI_PLAIN>(a, w, ep, m, n, k, (n + 255) / 256, s);

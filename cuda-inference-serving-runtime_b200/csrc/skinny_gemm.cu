@@ -61,6 +61,7 @@ struct SkinnyArgs {
     const int* positions; const int* token_req; const int* req_slot; const int* block_table; int table_width; int page_size;
     int hq; int hkv; int dim;
     int accumulate;                                // PLAIN: out += product
+    float out_mult;                                // PLAIN: the product is multiplied by it first (a constant factor of the residual branch)
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -394,7 +395,7 @@ __global__ void __launch_bounds__(EPI == EPI_PLAIN ? 256 : 512) skinny_kernel(co
             if (f >= a.n) continue;
             float v = 0.f;
             for (int q = 0; q < KS; ++q) v += red[((size_t)q * rows_cta + row) * mw + mrow];
-            v *= inv_rms(mrow);
+            v *= inv_rms(mrow) * a.out_mult;
             float* dst = a.out_f32 + (size_t)mrow * a.n + f;
             if (a.accumulate) v += e == tid ? there : *dst;          // the thread's first element was requested early
             *dst = v;
@@ -538,7 +539,7 @@ CISR_EXPORT int cisr_skinny_gemm(const void* w, int n, int k, const void* act, c
                                  const float* sin_t, int rot_half, int interleaved, void* q_out, void* k_cache,
                                  void* v_cache, const int* positions, const int* token_req, const int* req_slot,
                                  const int* block_table, int table_width, int page_size, int hq, int hkv, int dim,
-                                 int accumulate, void* stream) {
+                                 int accumulate, float out_mult, void* stream) {
     if (m <= 0) return 0;
     if (m > 64 || k % 8 || k <= 0 || n <= 0) return -2;
     if (epilogue == EPI_ROPE && (dim % 16 || dim > 256 || dim < 16 || n != (hq + 2 * hkv) * dim || 2 * rot_half > dim)) return -2;
@@ -546,7 +547,7 @@ CISR_EXPORT int cisr_skinny_gemm(const void* w, int n, int k, const void* act, c
     SkinnyArgs a;
     a.w = (const bf16*)w; a.n = n; a.k = k; a.act = (const bf16*)act; a.x = x; a.delta = delta; a.norm_w = norm_w;
     a.norm_w_bf16 = norm_w_dtype == CISR_BF16; a.eps = eps; a.x_out = x_out; a.rows = rows; a.m = m; a.rt = 1; a.ks = 1;
-    a.sums_in_smem = 0; a.accumulate = accumulate != 0 && epilogue == EPI_PLAIN;
+    a.sums_in_smem = 0; a.accumulate = accumulate != 0 && epilogue == EPI_PLAIN; a.out_mult = out_mult;
     a.out_f32 = out_f32; a.out_bf16 = (bf16*)out_bf16; a.inter = inter; a.cos_t = cos_t; a.sin_t = sin_t;
     a.rot_half = rot_half; a.interleaved = interleaved; a.q_out = (bf16*)q_out; a.k_cache = (bf16*)k_cache;
     a.v_cache = (bf16*)v_cache; a.positions = positions; a.token_req = token_req; a.req_slot = req_slot;

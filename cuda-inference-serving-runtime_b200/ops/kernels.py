@@ -1485,7 +1485,7 @@ def skinny_gemm(w: torch.Tensor, tokens: int, *, act: Optional[torch.Tensor] = N
                 delta: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
                 x_out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None, epilogue: int = EPI_PLAIN,
                 out: Optional[torch.Tensor] = None, rope: Optional[dict] = None, kind: str = "auto",
-                accumulate: bool = False) -> None:
+                accumulate: bool = False, out_mult: float = 1.0) -> None:
     """out = prologue(input) @ w^T with a fused epilogue; see csrc/skinny_gemm.cu and csrc/stream_gemm.cu.
 
     `kind`: "latency" (skinny_gemm.cu: a CTA per 16 output rows, weights straight to registers), "stream"
@@ -1494,7 +1494,8 @@ def skinny_gemm(w: torch.Tensor, tokens: int, *, act: Optional[torch.Tensor] = N
 
     Input is either `act` (bfloat16 [tokens, K]) or the norm prologue (`x`, optional `delta`, `norm_w`, `eps`,
     optional `x_out` receiving x + delta, optional `rows` picking rows of x).  PLAIN writes float `out`
-    [tokens, N], or with `accumulate` adds the product to what `out` holds (the residual stream); SWIGLU writes bfloat16 `out` [tokens, N / 2]; ROPE takes the `rope` dict (cos, sin, rot_half,
+    [tokens, N], or with `accumulate` adds the product to what `out` holds (the residual stream), in both cases times
+    `out_mult` (a constant factor of the residual branch); SWIGLU writes bfloat16 `out` [tokens, N / 2]; ROPE takes the `rope` dict (cos, sin, rot_half,
     interleaved, q_out, k_cache, v_cache, positions, token_req, req_slot, block_table, page_size, hq, hkv, dim).
     """
     _need(w, torch.bfloat16, "w", 2)
@@ -1539,9 +1540,9 @@ def skinny_gemm(w: torch.Tensor, tokens: int, *, act: Optional[torch.Tensor] = N
             int(bool(r.get("interleaved", False))), _p(r.get("q_out")), _p(r.get("k_cache")), _p(r.get("v_cache")),
             _p(r.get("positions")), _p(r.get("token_req")), _p(r.get("req_slot")), _p(r.get("block_table")),
             r["block_table"].shape[1] if rope else 0, int(r.get("page_size", 0)), int(r.get("hq", 0)), int(r.get("hkv", 0)),
-            int(r.get("dim", 0)), int(bool(accumulate)), _stream())
-    if accumulate and epilogue != EPI_PLAIN:
-        raise KernelError("skinny_gemm: only the plain epilogue adds into its output")
+            int(r.get("dim", 0)), int(bool(accumulate)), ctypes.c_float(out_mult), _stream())
+    if (accumulate or out_mult != 1.0) and epilogue != EPI_PLAIN:
+        raise KernelError("skinny_gemm: only the plain epilogue adds into its output or multiplies it")
     if kind not in ("auto", "latency", "stream"):
         raise KernelError(f"unknown kind {kind!r}")
     if kind == "stream" or (kind == "auto" and tokens <= STREAM_MAX_TOKENS and w.numel() * 2 >= STREAM_MIN_BYTES):
@@ -1607,15 +1608,16 @@ def tcgen05_ok(a: torch.Tensor, w: torch.Tensor, fused: bool = False) -> bool:
             and a.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, out_mult: float = 1.0) -> torch.Tensor:
     """out[M, N] (float) = a[M, K] @ w[N, K]^T on tcgen05 tensor cores fed by TMA (bfloat16 operands); with
-    `accumulate`, out += the product (the residual add as the product's epilogue)."""
+    `accumulate`, out += the product (the residual add as the product's epilogue); `out_mult`: the product is multiplied
+    by it first (a constant factor of the residual branch)."""
     _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 2); _need(out, torch.float32, "out", 2)
     m, k = a.shape
     n = w.shape[0]
     if w.shape[1] != k or out.shape != (m, n):
         raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
-    _check(_tcgen05().cisr_gemm_tcgen05(_p(a), _p(w), _p(out), m, n, k, int(accumulate), _stream()), "gemm_tcgen05")
+    _check(_tcgen05().cisr_gemm_tcgen05(_p(a), _p(w), _p(out), m, n, k, int(accumulate), ctypes.c_float(out_mult), _stream()), "gemm_tcgen05")
     return out
 
 
@@ -1815,7 +1817,7 @@ _DESCRIBE = {
     "sample": lambda logits, *rest, **kw: (int(logits.shape[0]), int(logits.shape[1])),
     "decode_advance": lambda *a, **kw: (),
     "gemm_library": _describe_gemm,
-    "gemm_tcgen05": _describe_gemm,
+    "gemm_tcgen05": lambda a, w, out, accumulate=False, out_mult=1.0: _describe_gemm(a, w),
     "gemm_tcgen05_swiglu": _describe_gemm,
     "gemm_tcgen05_rope": _describe_gemm,
     "skinny_gemm": lambda w, tokens, **kw: (int(tokens), int(w.shape[0]), int(w.shape[1]), int(kw.get("epilogue", EPI_PLAIN)),

@@ -88,6 +88,8 @@ class PendingNorm:
         # False where the arrangement multiplies the sub-block's output before it joins the stream: the part then hands its
         # output back instead of adding it to `stream.x` in the epilogue of its last product
         self.in_place_ok = True
+        # a constant the arrangement multiplies the sub-block's output by; a part that adds its output in place applies it
+        self.out_mult = 1.0
 
     def fusable(self) -> bool:
         # a pending output that still has to be scaled per channel is added by the norm's own kernel

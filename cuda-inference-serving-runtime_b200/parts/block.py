@@ -113,17 +113,24 @@ class PreNormScaledBlock:
         return {slot: getattr(self, slot) for slot in slots if getattr(self, slot) is not None}
 
     @staticmethod
-    def _run(part, h, *args):
-        h.in_place_ok = False          # the output is scaled on its way into the stream: no part adds it there itself
+    def _run(part, h, scale, *args):
+        """A factor per channel is applied on the output's way into the stream, so no part adds it there itself; one
+        constant for all channels (`scale.value`) can be the factor of a product's in-place add, and the part is told so."""
+        if scale.value is None:
+            h.in_place_ok = False
+        else:
+            h.out_mult = float(scale.value)
         return part.forward(h if part.accepts_pending_norm else h.materialize(), *args)
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
-        mixed = self._run(self.mixer, PendingNorm(stream, self.mixer_norm, self.dtype), ctx, cache)
-        stream.pending, stream.pending_scale = mixed, self.mixer_scale.weight
+        mixed = self._run(self.mixer, PendingNorm(stream, self.mixer_norm, self.dtype), self.mixer_scale, ctx, cache)
+        if mixed is not None:          # None: the mixer added its output, multiplied, to the stream itself
+            stream.pending, stream.pending_scale = mixed, self.mixer_scale.weight
         if self.feed_forward is not None:
             h = PendingNorm(stream, self.feed_forward_norm, self.dtype)
             if getattr(self.feed_forward, "applies_output_scale", False):
-                stream.pending = self._run(self.feed_forward, h, ctx, self.feed_forward_scale.weight)
+                stream.pending = self._run(self.feed_forward, h, self.feed_forward_scale, ctx, self.feed_forward_scale.weight)
             else:
-                out = self._run(self.feed_forward, h, ctx)
-                stream.pending, stream.pending_scale = out, self.feed_forward_scale.weight
+                out = self._run(self.feed_forward, h, self.feed_forward_scale, ctx)
+                if out is not None:
+                    stream.pending, stream.pending_scale = out, self.feed_forward_scale.weight

@@ -29,7 +29,7 @@ from ..config.spec import CacheUse
 from ..ops import kernels
 from .attention import ATTENTION_PLAN_KEY, attention_step_plan, paged_attention
 from .base import MIXERS, POSITIONS, Mixer, TensorNeed, build_part, register
-from .linear import as_tensor, linear
+from .linear import as_tensor, linear, linear_to_stream
 
 DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "o": "o", "q_conv": "q.conv", "k_conv": "k.conv", "v_conv": "v.conv",
                  "lq1": "lq1", "lk1": "lk1", "lq2": "lq2", "lk2": "lk2"}
@@ -41,7 +41,9 @@ class DiffAttention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, key_dim, value_dim, scale, diff, eps, conv (taps; 1: one weight per
     channel, 0: no convolution and no tensors for it), gate (bool, default True), position (PartSpec of a rotary encoding
     over the leading coordinates of each map, default none; only without a convolution), window (None or int), keep_first
-    (int), shared_kv (bool: no key/value tensors, the pages of another run entry), names."""
+    (int), shared_kv (bool: no key/value tensors, the pages of another run entry), in_place (bool, default False: the
+    mixer takes its input as a pending norm and its output projection may add its result to the residual stream in
+    place, where the arrangement allows that), names."""
 
     graph_safe = True
 
@@ -55,6 +57,7 @@ class DiffAttention(Mixer):
         self.eps = float(spec["eps"])
         self.taps = int(spec.get("conv", 1))
         self.gate = bool(spec.get("gate", True))
+        self.accepts_pending_norm = bool(spec.get("in_place", False))
         self.position = build_part(POSITIONS, spec["position"], dtype, "position encoding") if spec.get("position") is not None else None
         self.window = spec.get("window")
         self.keep_first = int(spec.get("keep_first") or 0)
@@ -148,15 +151,15 @@ class DiffAttention(Mixer):
                                    k_cache=cache.k if cache.write else None, v_cache=cache.v if cache.write else None,
                                    block_table=cache.block_table, page_size=cache.page_size, hq=self.hq, hkv=self.hkv,
                                    key_dim=self.key_dim, value_dim=self.value_dim)
-            return self.attend(q, proj, ctx, cache)
+            return self.attend(q, proj, ctx, cache, h)
         kernels.diff_rows(proj, self.conv_w, self.taps, cache.state, token_req=ctx.token_req, req_slot=ctx.req_slot, q_start=ctx.q_start,
                           positions=ctx.positions, q_out=q, k_cache=cache.k if cache.write else None,
                           v_cache=cache.v if cache.write else None, block_table=cache.block_table, page_size=cache.page_size,
                           hq=self.hq, hkv=self.hkv, key_dim=self.key_dim, value_dim=self.value_dim)
         kernels.conv_keep(proj, cache.state, ctx.req_slot, ctx.q_start, ctx.q_len, ctx.n_requests, self.taps, self.channels)
-        return self.attend(q, proj, ctx, cache)
+        return self.attend(q, proj, ctx, cache, h)
 
-    def attend(self, q, proj, ctx, cache):
+    def attend(self, q, proj, ctx, cache, h):
         """The two maps of every head over the pages, their combination, the head norm, the gate and the output projection."""
         tokens = ctx.n_tokens
         mixed = paged_attention(ctx.plan_for(self), q, cache.k, cache.v, cache, ctx, 2 * self.hq, self.hkv, self.scale, self.window,
@@ -164,4 +167,4 @@ class DiffAttention(Mixer):
         gated = torch.empty((tokens, self.hq * self.value_dim), dtype=self.dtype, device=ctx.device)
         kernels.diff_combine(mixed, proj if self.gate else None, self.channels, gated, self.hq, self.value_dim, self.lam, self.eps,
                              1.0 - self.diff)
-        return linear(gated, self.o)
+        return linear_to_stream(gated, self.o, h)

@@ -34,7 +34,7 @@ from ..config.spec import CacheUse
 from ..ops import kernels
 from .attention import ATTENTION_PLAN_KEY, attention_step_plan, paged_attention
 from .base import MIXERS, POSITIONS, Mixer, TensorNeed, build_part, register
-from .linear import as_tensor, linear, norm_fusable
+from .linear import as_tensor, linear, linear_to_stream, norm_fusable
 
 ROW_STEP = 16          # cache rows are padded to a multiple of this (the attention kernels' head sizes)
 DEFAULT_NAMES = {"sink": "sink", "q": "q_proj.weight", "q_down": "q_down.weight", "q_norm": "q_norm.weight", "q_up": "q_up.weight",
@@ -166,11 +166,11 @@ class LatentAttention(Mixer):
         if few:      # W_vup_h (weighted sum of latents), gate and rounding in one row kernel
             values = kernels.latent_values(mixed, self.v_up, proj if self.gate else None, self.gate_col,
                                            torch.empty((tokens, H * self.vdim), dtype=self.dtype, device=device))
-            return linear(values, self.o)
+            return linear_to_stream(values, self.o, h)
         values = torch.empty((tokens, H, self.vdim), dtype=torch.float32, device=device)
         kernels.gemm_heads(mixed, self.v_up, values, w_is_nk=True)             # W_vup_h (weighted sum of latents)
         values = values.view(tokens, H * self.vdim)
         if self.gate or self.dtype != torch.float32:
             values = kernels.latent_gate(values, proj if self.gate else None, self.gate_col,
                                          torch.empty((tokens, H * self.vdim), dtype=self.dtype, device=device))
-        return linear(values, self.o)
+        return linear_to_stream(values, self.o, h)

@@ -20,7 +20,7 @@ from ..config.spec import CacheUse
 from ..ops import kernels
 from .base import MIXERS, Mixer, TensorNeed, register
 from .feedforward import pad_columns
-from .linear import as_tensor, linear
+from .linear import as_tensor, linear, linear_to_stream
 
 CHUNKED_FROM = kernels.LIGHTNING_CHUNK
 LIGHTNING_PLAN_KEY = ("lightning_chunks", CHUNKED_FROM)
@@ -41,6 +41,7 @@ class LightningAttention(Mixer):
     # forward reads the step through device tensors only.  A captured step's warm-up run outside the graph would advance
     # the state once too often: the graph code keeps the state tensors and puts them back after it (engine/graph.py).
     graph_safe = True
+    accepts_pending_norm = True      # for its last product, which may add its result to the residual stream in place
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
@@ -103,4 +104,4 @@ class LightningAttention(Mixer):
         make = torch.zeros if width != self.nv else torch.empty
         gated = make((tokens, width), dtype=self.dtype, device=ctx.device)
         kernels.lightning_output(o, proj, 2 * self.nqk + self.nv, self.norm, self.eps, gated)
-        return linear(gated, self.o)
+        return linear_to_stream(gated, self.o, h)

@@ -73,13 +73,16 @@ def linear_to_stream(a: torch.Tensor, w: torch.Tensor, h):
     In place needs the stream's current tensor (`stream_target`) and a product kernel with the add as its epilogue:
     the weight-streaming kernels for few tokens, the tcgen05 product for many.  The sum is the same single float add
     per element that the next norm would otherwise make, so the logits do not change with the path; the norm after
-    it then reads one tensor instead of two."""
+    it then reads one tensor instead of two.  Where the arrangement multiplies the sub-block's output by one constant
+    (`h.out_mult`), the in-place add multiplies the product by it in the same epilogue; the product that is handed back
+    is never multiplied (the arrangement does that when it adds it)."""
     x = stream_target(h, a.shape[0], w.shape[0])
     if x is not None and a.shape[0] > 0:
+        mult = float(getattr(h, "out_mult", 1.0))
         if kernels.skinny_ok(a.shape[0], w) and a.dtype == torch.bfloat16:
-            kernels.skinny_gemm(w, a.shape[0], act=a, epilogue=kernels.EPI_PLAIN, out=x, accumulate=True)
+            kernels.skinny_gemm(w, a.shape[0], act=a, epilogue=kernels.EPI_PLAIN, out=x, accumulate=True, out_mult=mult)
             return None
         if kernels.tcgen05_ok(a, w):
-            kernels.gemm_tcgen05(a, w, x, accumulate=True)
+            kernels.gemm_tcgen05(a, w, x, accumulate=True, out_mult=mult)
             return None
     return linear(a, w)

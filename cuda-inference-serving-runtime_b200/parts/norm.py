@@ -58,7 +58,7 @@ class ScalarRMSNorm(RMSNorm):
 
 @register(NORMS, "rms_norm_offset")
 class OffsetRMSNorm(RMSNorm):
-    """x / sqrt(mean(x^2) + eps) * (1 + w): the weight is stored around zero.  params: size, eps; weight_name.  1 + w is
+    """x / sqrt(mean(x^2) + eps) * (1 + w): the tensor holds the factor's offset from one.  params: size, eps; weight_name.  1 + w is
     formed once at load, in float (it has no exact bfloat16 form), so every kernel that takes RMSNorm takes this one as
     it is: their weights may be float whatever the storage type."""
 

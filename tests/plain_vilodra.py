@@ -19,7 +19,7 @@ def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def layer_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
-    """The norm of the layers and of the model's end: its weight is stored around zero."""
+    """The norm of the layers and of the model's end: the tensor holds the factor's offset from one."""
     return rms(x, eps) * (1.0 + weight)
 
 

@@ -134,7 +134,7 @@ def tensor_shapes(cfg: dict) -> dict:
 def make_weights(cfg: dict, seed: int, gain: float = 1.0) -> dict:
     """Seeded weights, every value representable in bfloat16 (so a bfloat16 engine and a float oracle start alike).
     `gain` scales the query projections of the softmax mixers (a larger one makes the softmax peaked).  Norm weights
-    (stored around zero), sinks, the lambda vectors and routers are spread widely, so that leaving one out, or using a
+    (offsets from one), sinks, the lambda vectors and routers are spread widely, so that leaving one out, or using a
     weight without its offset, moves the logits."""
     rng = np.random.default_rng(seed)
     out = {}
