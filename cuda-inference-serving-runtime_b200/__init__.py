@@ -1,4 +1,4 @@
-"""B200-native inference engine for the Llama dense decoder, Zurolorn and Ronolorn (one GPU).
+"""B200-native inference engine for the Llama dense decoder, Zurolorn, Ronolorn, Gipozen and Vilodra (one GPU).
 
     from cisr_b200 import Model, Engine, Request
     model = Model.from_pretrained("path/to/model", dtype="bfloat16")    # or Model.from_config("smollm2-135m", seed=0)

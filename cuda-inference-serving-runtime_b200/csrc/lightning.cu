@@ -15,9 +15,10 @@
 //           chunk of n tokens and S0 the state before it:
 //               o_t = decay^(t+1) S0^T q_t + sum_{i <= t} decay^(t-i) (q_t . k_i) v_i
 //               S   = decay^n S0 + sum_i decay^(n-1-i) k_i v_i^T
-//           three small float products per chunk in shared memory (scores, read-out, state), register tiles of 4 x 4 and
-//           4 x CPT.  The columns of S are independent: a CTA takes CB = 16 CPT value columns of one head and recomputes
-//           the chunk's scores for them.
+//           The second sum of S (a chunk's gain) needs no state, so it is made for every chunk of the step at once; a short
+//           scan then carries the state from chunk to chunk, element by element; and the read-outs of every chunk are made
+//           at once from the state before each.  Small float products in shared memory, register tiles of 4 x 4 and
+//           4 x CPT; a CTA takes CB = 16 CPT value columns of one head and one chunk.
 #include "common.cuh"
 
 static bool g_pdl = false;
@@ -82,215 +83,287 @@ lightning_walk_kernel(const float* __restrict__ proj, int stride, int q_col, int
 }
 
 // ---------------------------------------------------------------- chunk by chunk
-// grid (requests, heads, value columns / CB), 256 threads as 16 x 16: thread (ty, tx) owns rows 4 ty .. 4 ty + 3 of a
-// 64-row tile and columns 4 tx .. (scores) or CPT tx .. (read-out, state).  Shared memory (floats), LD = C + 4:
+// Three launches over the chunks of the step's long portions (chunk_req, chunk_t0: a chunk's request and its first token
+// inside the portion; req_chunk0: a request's first chunk), with a scratch of one state-sized block per (chunk, head):
+//   gains   (chunk, head, CB value columns): the chunk's own contribution to the state, sum_i decay^(n-1-i) k_i v_i^T,
+//           into the chunk's scratch block [key_dim][value_dim].  Every chunk at once.
+//   scan    (request, head): walks the request's chunks element by element: the scratch block receives the state BEFORE
+//           its chunk, the running state becomes decay^n S + gain; the last one goes back to the request's slot.
+//   reads   (chunk, head, CB value columns): the read-outs, decay^(t+1) S0^T q_t + sum_{i<=t} decay^(t-i) (q_t . k_i) v_i
+//           with S0 from the scratch.  Every chunk at once.
+// 256 threads as 16 x 16: thread (ty, tx) owns rows 4 ty .. 4 ty + 3 of a 64-row tile and columns 4 tx .. (scores) or
+// CPT tx .. (read-outs, gains).  Shared memory (floats), LD = C + 4:
 //   Qt, Kt [dP][LD]   silu(q), silu(k) of the chunk, coordinate-major (dP: key_dim rounded up to 4), zero beyond the portion
 //   P [C][LD]         decayed scores, zero above the diagonal
 //   V [C][CB]         silu(v) of the CTA's columns
-//   S [dP][CB]        the state's columns
+//   S [dP][CB]        the state's columns before the chunk (in Kt's place once the scores are made)
 //   pw [C + 1]        powers of the decay
 constexpr int C = LIGHTNING_CHUNK, LD = C + 4;
+
+struct ChunkArgs {
+    const float* proj; int stride, q_col, k_col, v_col;
+    const float* decay;
+    float* state; long long state_stride;
+    const int* req_slot; const int* q_start; const int* q_len;
+    const int* chunk_req; const int* chunk_t0; const int* req_chunk0;
+    float* scratch;                       // [chunks][heads][key_dim][value_dim]
+    float* o; int heads, key_dim, value_dim, least;
+};
+
+// silu of one projection of the chunk's tokens, coordinate-major into dst [dP][LD]; zero beyond the portion and the width
+__device__ __forceinline__ void stage_transposed(const ChunkArgs& a, int col0, int token0, int n, int dP, float* dst) {
+    for (int i = threadIdx.x; i < C * dP; i += 256) {
+        const int t = i / dP, kk = i - t * dP;
+        dst[kk * LD + t] = (t < n && kk < a.key_dim) ? silu_f(a.proj[(size_t)(token0 + t) * a.stride + col0 + kk]) : 0.f;
+    }
+}
+// silu(v) of the CTA's columns into V [C][CB], each row times weight(t) (zero beyond the portion and the width)
+template <int CB, typename W>
+__device__ __forceinline__ void stage_values(const ChunkArgs& a, int h, int c0, int token0, int n, float* V, W weight) {
+    for (int i = threadIdx.x; i < C * CB; i += 256) {
+        const int t = i / CB, c = i - t * CB;
+        V[i] = (t < n && c0 + c < a.value_dim)
+                   ? silu_f(a.proj[(size_t)(token0 + t) * a.stride + a.v_col + h * a.value_dim + c0 + c]) * weight(t) : 0.f;
+    }
+}
+__device__ __forceinline__ void stage_powers(float decay, float* pw) {
+    const float lg = logf(decay);
+    for (int j = threadIdx.x; j <= C; j += 256) pw[j] = j ? expf((float)j * lg) : 1.f;
+}
+
+// CPT neighbouring floats of shared memory in one access (the address is a multiple of 4 CPT bytes)
 template <int CPT>
-__global__ void __launch_bounds__(256)
-lightning_chunk_kernel(const float* __restrict__ proj, int stride, int q_col, int k_col, int v_col, const float* __restrict__ decay,
-                       float* __restrict__ state, long long state_stride, const int* __restrict__ req_slot,
-                       const int* __restrict__ q_start, const int* __restrict__ q_len, float* __restrict__ o, int heads, int key_dim,
-                       int value_dim, int least) {
+__device__ __forceinline__ void load_run(const float* __restrict__ p, float (&v)[CPT]) {
+    if (CPT == 4) { const float4 x = *reinterpret_cast<const float4*>(p); v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; }
+    else if (CPT == 2) { const float2 x = *reinterpret_cast<const float2*>(p); v[0] = x.x; v[1] = x.y; }
+    else v[0] = p[0];
+}
+
+template <int CPT>
+__global__ void __launch_bounds__(256) lightning_gains_kernel(ChunkArgs a) {
     constexpr int CB = 16 * CPT;
     extern __shared__ __align__(16) float lightning_smem[];
     pdl_trigger();
     pdl_wait();
-    const int r = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * CB, tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
-    const int n_all = q_len[r];
-    if (n_all < least) return;
-    const int dP = (key_dim + 3) & ~3;
-    float* Qt = lightning_smem;
-    float* Kt = Qt + (size_t)dP * LD;
-    float* P = Kt + (size_t)dP * LD;
-    float* V = P + (size_t)C * LD;
-    float* S = V + (size_t)C * CB;
-    float* pw = S + (size_t)dP * CB;
-    float* slot_state = state + (size_t)req_slot[r] * state_stride + (size_t)h * value_dim * key_dim;
-    for (int i = tid; i < dP * CB; i += 256) {
-        const int c = i / dP, row = i - c * dP;          // a column of the state is contiguous in memory
-        S[row * CB + c] = (row < key_dim && c0 + c < value_dim) ? slot_state[(size_t)(c0 + c) * key_dim + row] : 0.f;
-    }
-    const float lg = logf(decay[h]);
-    for (int j = tid; j <= C; j += 256) pw[j] = j ? expf((float)j * lg) : 1.f;
-    const int t_first = q_start[r];
-    for (int t0 = 0; t0 < n_all; t0 += C) {
-        const int n = min(C, n_all - t0);
-        __syncthreads();                                  // the chunk before is done with Qt, Kt, V; S and pw are written
-        for (int i = tid; i < C * dP; i += 256) {
-            const int t = i / dP, kk = i - t * dP;
-            float q = 0.f, k = 0.f;
-            if (t < n && kk < key_dim) {
-                const float* row_p = proj + (size_t)(t_first + t0 + t) * stride + h * key_dim + kk;
-                q = silu_f(row_p[q_col]);
-                k = silu_f(row_p[k_col]);
-            }
-            Qt[kk * LD + t] = q;
-            Kt[kk * LD + t] = k;
-        }
-        for (int i = tid; i < C * CB; i += 256) {
-            const int t = i / CB, c = i - t * CB;
-            V[i] = (t < n && c0 + c < value_dim) ? silu_f(proj[(size_t)(t_first + t0 + t) * stride + v_col + h * value_dim + c0 + c]) : 0.f;
-        }
-        __syncthreads();
-        // scores of the chunk: P[t][i] = decay^(t - i) (q_t . k_i) for i <= t
-        {
-            float acc[4][4] = {};
-            if (tx <= ty) {                                // tiles above the diagonal hold nothing
-                for (int kk = 0; kk < dP; ++kk) {
-                    const float4 a = *reinterpret_cast<const float4*>(Qt + kk * LD + 4 * ty);
-                    const float4 b = *reinterpret_cast<const float4*>(Kt + kk * LD + 4 * tx);
-                    const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-                    for (int x = 0; x < 4; ++x)
-#pragma unroll
-                        for (int y = 0; y < 4; ++y) acc[x][y] += av[x] * bv[y];
-                }
-            }
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                const int t = 4 * ty + x;
-                float4 out;
-                float* ov = reinterpret_cast<float*>(&out);
-#pragma unroll
-                for (int y = 0; y < 4; ++y) { const int i = 4 * tx + y; ov[y] = i <= t ? acc[x][y] * pw[t - i] : 0.f; }
-                *reinterpret_cast<float4*>(P + t * LD + 4 * tx) = out;
-            }
-        }
-        __syncthreads();
-        // read-out: o_t = decay^(t+1) S0^T q_t + sum_i P[t][i] v_i
-        {
-            float acc[4][CPT] = {}, carried[4][CPT] = {};
-            for (int i = 0; i < 4 * ty + 4; i += 4) {      // P holds nothing right of the diagonal
-                float4 p[4];
-#pragma unroll
-                for (int x = 0; x < 4; ++x) p[x] = *reinterpret_cast<const float4*>(P + (4 * ty + x) * LD + i);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float v[CPT];
-#pragma unroll
-                    for (int y = 0; y < CPT; ++y) v[y] = V[(i + j) * CB + CPT * tx + y];
-#pragma unroll
-                    for (int x = 0; x < 4; ++x) {
-                        const float pv = reinterpret_cast<const float*>(&p[x])[j];
-#pragma unroll
-                        for (int y = 0; y < CPT; ++y) acc[x][y] += pv * v[y];
-                    }
-                }
-            }
-            for (int row = 0; row < dP; ++row) {
-                const float4 a = *reinterpret_cast<const float4*>(Qt + row * LD + 4 * ty);
-                const float av[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-                for (int y = 0; y < CPT; ++y) {
-                    const float s = S[row * CB + CPT * tx + y];
-#pragma unroll
-                    for (int x = 0; x < 4; ++x) carried[x][y] += av[x] * s;
-                }
-            }
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                const int t = 4 * ty + x;
-                if (t >= n) continue;
-#pragma unroll
-                for (int y = 0; y < CPT; ++y) {
-                    const int c = c0 + CPT * tx + y;
-                    if (c < value_dim)
-                        o[(size_t)(t_first + t0 + t) * heads * value_dim + h * value_dim + c] = pw[t + 1] * carried[x][y] + acc[x][y];
-                }
-            }
-        }
-        __syncthreads();                                  // every read-out has used the old state
-        // state: S = decay^n S0 + sum_i decay^(n-1-i) k_i v_i^T   (v_i is scaled in place first)
-        for (int i = tid; i < C * CB; i += 256) { const int t = i / CB; V[i] = t < n ? V[i] * pw[n - 1 - t] : 0.f; }
-        __syncthreads();
-        for (int row0 = 0; row0 < dP; row0 += 64) {
-            const int row = row0 + 4 * ty;
-            if (row >= dP) continue;                       // dP is a multiple of 4: a thread's four rows exist together
-            float acc[4][CPT] = {};
-            for (int i = 0; i < C; i += 4) {
-                float4 k[4];
-#pragma unroll
-                for (int x = 0; x < 4; ++x) k[x] = *reinterpret_cast<const float4*>(Kt + (row + x) * LD + i);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float v[CPT];
-#pragma unroll
-                    for (int y = 0; y < CPT; ++y) v[y] = V[(i + j) * CB + CPT * tx + y];
-#pragma unroll
-                    for (int x = 0; x < 4; ++x) {
-                        const float kv = reinterpret_cast<const float*>(&k[x])[j];
-#pragma unroll
-                        for (int y = 0; y < CPT; ++y) acc[x][y] += kv * v[y];
-                    }
-                }
-            }
-#pragma unroll
-            for (int x = 0; x < 4; ++x)
-#pragma unroll
-                for (int y = 0; y < CPT; ++y) {
-                    float* s = S + (row + x) * CB + CPT * tx + y;
-                    *s = pw[n] * *s + acc[x][y];
-                }
-        }
-    }
+    const int chunk = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * CB, ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    const int r = a.chunk_req[chunk], t0 = a.chunk_t0[chunk], n = min(C, a.q_len[r] - t0), token0 = a.q_start[r] + t0;
+    const int dP = (a.key_dim + 3) & ~3;
+    float* Kt = lightning_smem;
+    float* V = Kt + (size_t)dP * LD;
+    float* pw = V + (size_t)C * CB;
+    stage_powers(a.decay[h], pw);
+    stage_transposed(a, a.k_col + h * a.key_dim, token0, n, dP, Kt);
     __syncthreads();
-    for (int i = tid; i < dP * CB; i += 256) {
-        const int c = i / dP, row = i - c * dP;
-        if (row < key_dim && c0 + c < value_dim) slot_state[(size_t)(c0 + c) * key_dim + row] = S[row * CB + c];
+    stage_values<CB>(a, h, c0, token0, n, V, [&](int t) { return pw[n - 1 - t]; });
+    __syncthreads();
+    float* block = a.scratch + ((size_t)chunk * a.heads + h) * a.key_dim * a.value_dim;
+    for (int row0 = 0; row0 < dP; row0 += 64) {
+        const int row = row0 + 4 * ty;
+        if (row >= dP) continue;                       // dP is a multiple of 4: a thread's four rows exist together
+        float acc[4][CPT] = {};
+        for (int i = 0; i < C; i += 4) {
+            float4 k[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) k[x] = *reinterpret_cast<const float4*>(Kt + (row + x) * LD + i);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float v[CPT];
+                load_run<CPT>(V + (i + j) * CB + CPT * tx, v);
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const float kv = reinterpret_cast<const float*>(&k[x])[j];
+#pragma unroll
+                    for (int y = 0; y < CPT; ++y) acc[x][y] += kv * v[y];
+                }
+            }
+        }
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+#pragma unroll
+            for (int y = 0; y < CPT; ++y) {
+                const int c = c0 + CPT * tx + y;
+                if (row + x < a.key_dim && c < a.value_dim) block[(size_t)(row + x) * a.value_dim + c] = acc[x][y];
+            }
     }
 }
 
-static size_t chunk_smem(int key_dim, int cb) {
-    const size_t dP = (size_t)((key_dim + 3) & ~3);
-    return sizeof(float) * (2 * dP * LD + (size_t)C * LD + (size_t)C * cb + dP * cb + C + 1 + 3);
+// grid (requests, heads, elements / 256): thread e owns element (row, col) = (e / value_dim, e % value_dim) of the head's state
+__global__ void __launch_bounds__(256) lightning_scan_kernel(ChunkArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x, h = blockIdx.y, e = blockIdx.z * 256 + threadIdx.x;
+    const int n_all = a.q_len[r];
+    if (n_all < a.least || e >= a.key_dim * a.value_dim) return;
+    const int row = e / a.value_dim, col = e - row * a.value_dim;
+    float* kept = a.state + (size_t)a.req_slot[r] * a.state_stride + ((size_t)h * a.value_dim + col) * a.key_dim + row;
+    float S = *kept;
+    const float lg = logf(a.decay[h]), whole = expf((float)C * lg);
+    const size_t step = (size_t)a.heads * a.key_dim * a.value_dim;
+    float* block = a.scratch + ((size_t)a.req_chunk0[r] * a.heads + h) * a.key_dim * a.value_dim + e;
+    const int chunks = (n_all + C - 1) / C;
+    float gain = block[0];
+    for (int c = 0; c < chunks; ++c) {
+        const float next = c + 1 < chunks ? block[(size_t)(c + 1) * step] : 0.f;      // on its way during this chunk's step
+        const int n = min(C, n_all - c * C);
+        block[(size_t)c * step] = S;
+        S = (n == C ? whole : expf((float)n * lg)) * S + gain;
+        gain = next;
+    }
+    *kept = S;
 }
 
 template <int CPT>
-static int launch_chunks(const float* proj, int stride, int q_col, int k_col, int v_col, const float* decay, float* state,
-                         long long state_stride, const int* req_slot, const int* q_start, const int* q_len, float* o, int heads,
-                         int key_dim, int value_dim, int n_req, int least, cudaStream_t s) {
-    const size_t smem = chunk_smem(key_dim, 16 * CPT);
-    static size_t allowed = 0;
-    if (smem > allowed) {
-        if (cudaFuncSetAttribute(lightning_chunk_kernel<CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-            cudaGetLastError();
-            return -3;
+__global__ void __launch_bounds__(256) lightning_reads_kernel(ChunkArgs a) {
+    constexpr int CB = 16 * CPT;
+    extern __shared__ __align__(16) float lightning_smem[];
+    pdl_trigger();
+    pdl_wait();
+    const int chunk = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * CB, tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const int r = a.chunk_req[chunk], t0 = a.chunk_t0[chunk], n = min(C, a.q_len[r] - t0), token0 = a.q_start[r] + t0;
+    const int dP = (a.key_dim + 3) & ~3;
+    float* Qt = lightning_smem;
+    float* Kt = Qt + (size_t)dP * LD;                     // later S [dP][CB], CB <= LD
+    float* P = Kt + (size_t)dP * LD;
+    float* V = P + (size_t)C * LD;
+    float* pw = V + (size_t)C * CB;
+    float* S = Kt;
+    stage_powers(a.decay[h], pw);
+    stage_transposed(a, a.q_col + h * a.key_dim, token0, n, dP, Qt);
+    stage_transposed(a, a.k_col + h * a.key_dim, token0, n, dP, Kt);
+    stage_values<CB>(a, h, c0, token0, n, V, [](int) { return 1.f; });
+    __syncthreads();
+    // scores of the chunk: P[t][i] = decay^(t - i) (q_t . k_i) for i <= t
+    {
+        float acc[4][4] = {};
+        if (tx <= ty) {                                // tiles above the diagonal hold nothing
+            for (int kk = 0; kk < dP; ++kk) {
+                const float4 q = *reinterpret_cast<const float4*>(Qt + kk * LD + 4 * ty);
+                const float4 k = *reinterpret_cast<const float4*>(Kt + kk * LD + 4 * tx);
+                const float qv[4] = {q.x, q.y, q.z, q.w}, kv[4] = {k.x, k.y, k.z, k.w};
+#pragma unroll
+                for (int x = 0; x < 4; ++x)
+#pragma unroll
+                    for (int y = 0; y < 4; ++y) acc[x][y] += qv[x] * kv[y];
+            }
         }
-        allowed = smem;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int t = 4 * ty + x;
+            float4 out;
+            float* ov = reinterpret_cast<float*>(&out);
+#pragma unroll
+            for (int y = 0; y < 4; ++y) { const int i = 4 * tx + y; ov[y] = i <= t ? acc[x][y] * pw[t - i] : 0.f; }
+            *reinterpret_cast<float4*>(P + t * LD + 4 * tx) = out;
+        }
     }
-    return launch_kernel(lightning_chunk_kernel<CPT>, dim3(n_req, heads, (value_dim + 16 * CPT - 1) / (16 * CPT)), dim3(256), smem, s, g_pdl,
-                         proj, stride, q_col, k_col, v_col, decay, state, state_stride, req_slot, q_start, q_len, o, heads, key_dim,
-                         value_dim, least);
+    __syncthreads();                                      // the scores are made: the keys' place takes the state's columns
+    const float* block = a.scratch + ((size_t)chunk * a.heads + h) * a.key_dim * a.value_dim;
+    for (int i = tid; i < dP * CB; i += 256) {
+        const int row = i / CB, c = i - row * CB;
+        S[i] = (row < a.key_dim && c0 + c < a.value_dim) ? block[(size_t)row * a.value_dim + c0 + c] : 0.f;
+    }
+    __syncthreads();
+    float acc[4][CPT] = {}, carried[4][CPT] = {};
+    for (int i = 0; i < 4 * ty + 4; i += 4) {             // P holds nothing right of the diagonal
+        float4 p[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) p[x] = *reinterpret_cast<const float4*>(P + (4 * ty + x) * LD + i);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float v[CPT];
+            load_run<CPT>(V + (i + j) * CB + CPT * tx, v);
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const float pv = reinterpret_cast<const float*>(&p[x])[j];
+#pragma unroll
+                for (int y = 0; y < CPT; ++y) acc[x][y] += pv * v[y];
+            }
+        }
+    }
+    for (int row = 0; row < dP; ++row) {
+        const float4 q = *reinterpret_cast<const float4*>(Qt + row * LD + 4 * ty);
+        const float qv[4] = {q.x, q.y, q.z, q.w};
+        float sv[CPT];
+        load_run<CPT>(S + row * CB + CPT * tx, sv);
+#pragma unroll
+        for (int y = 0; y < CPT; ++y)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) carried[x][y] += qv[x] * sv[y];
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+        const int t = 4 * ty + x;
+        if (t >= n) continue;
+#pragma unroll
+        for (int y = 0; y < CPT; ++y) {
+            const int c = c0 + CPT * tx + y;
+            if (c < a.value_dim) a.o[(size_t)(token0 + t) * a.heads * a.value_dim + h * a.value_dim + c] = pw[t + 1] * carried[x][y] + acc[x][y];
+        }
+    }
 }
 
-// The recurrence for a step: `n_long` requests bring at least `least` tokens (they run chunk by chunk), `n_short` fewer
-// (token by token); least <= 0: every request token by token.  o float [tokens, heads * value_dim].
+static size_t gains_smem(int key_dim, int cb) {
+    const size_t dP = (size_t)((key_dim + 3) & ~3);
+    return sizeof(float) * (dP * LD + (size_t)C * cb + C + 1 + 3);
+}
+static size_t reads_smem(int key_dim, int cb) {
+    const size_t dP = (size_t)((key_dim + 3) & ~3);
+    return sizeof(float) * (2 * dP * LD + (size_t)C * LD + (size_t)C * cb + C + 1 + 3);
+}
+
+template <int CPT>
+static int launch_chunks(const ChunkArgs& a, int n_req, int n_chunks, cudaStream_t s) {
+    const int cb = 16 * CPT, slabs = (a.value_dim + cb - 1) / cb;
+    const size_t smem_g = gains_smem(a.key_dim, cb), smem_r = reads_smem(a.key_dim, cb);
+    static size_t allowed_g = 0, allowed_r = 0;
+    if (smem_g > allowed_g) {
+        if (cudaFuncSetAttribute(lightning_gains_kernel<CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_g) != cudaSuccess) { cudaGetLastError(); return -3; }
+        allowed_g = smem_g;
+    }
+    if (smem_r > allowed_r) {
+        if (cudaFuncSetAttribute(lightning_reads_kernel<CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_r) != cudaSuccess) { cudaGetLastError(); return -3; }
+        allowed_r = smem_r;
+    }
+    int st = launch_kernel(lightning_gains_kernel<CPT>, dim3(n_chunks, a.heads, slabs), dim3(256), smem_g, s, g_pdl, a);
+    if (st) return st;
+    st = launch_kernel(lightning_scan_kernel, dim3(n_req, a.heads, (a.key_dim * a.value_dim + 255) / 256), dim3(256), 0, s, g_pdl, a);
+    if (st) return st;
+    return launch_kernel(lightning_reads_kernel<CPT>, dim3(n_chunks, a.heads, slabs), dim3(256), smem_r, s, g_pdl, a);
+}
+
+CISR_EXPORT long long cisr_lightning_scratch_floats(int n_chunks, int heads, int key_dim, int value_dim) {
+    return (long long)n_chunks * heads * key_dim * value_dim;
+}
+
+// The recurrence for a step: the requests that bring at least `least` tokens run chunk by chunk (`n_chunks` chunks listed in
+// chunk_req / chunk_t0, a request's first one in req_chunk0; scratch as cisr_lightning_scratch_floats says), the `n_short`
+// others token by token; least <= 0: every request token by token.  o float [tokens, heads * value_dim].
 CISR_EXPORT int cisr_lightning_recurrence(const float* proj, int stride, int q_col, int k_col, int v_col, const float* decay, float* state,
                                           long long state_stride, const int* req_slot, const int* q_start, const int* q_len, float* o,
-                                          int heads, int key_dim, int value_dim, int n_req, int least, int n_long, int n_short,
+                                          int heads, int key_dim, int value_dim, int n_req, int least, int n_chunks, int n_short,
+                                          const int* chunk_req, const int* chunk_t0, const int* req_chunk0, float* scratch,
                                           int columns_per_cta, void* stream) {
     if (n_req <= 0) return 0;
     if (key_dim <= 0 || key_dim > MAX_KEY_DIM || value_dim <= 0 || heads <= 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     int st = 0;
-    if (least > 0 && n_long > 0) {
-        // as many value columns per CTA as still leave the device's SMs a CTA each (the scores are recomputed per CTA)
+    if (least > 0 && n_chunks > 0) {
+        if (!chunk_req || !chunk_t0 || !req_chunk0 || !scratch) return -2;
+        ChunkArgs a;
+        a.proj = proj; a.stride = stride; a.q_col = q_col; a.k_col = k_col; a.v_col = v_col; a.decay = decay; a.state = state;
+        a.state_stride = state_stride; a.req_slot = req_slot; a.q_start = q_start; a.q_len = q_len; a.chunk_req = chunk_req;
+        a.chunk_t0 = chunk_t0; a.req_chunk0 = req_chunk0; a.scratch = scratch; a.o = o; a.heads = heads; a.key_dim = key_dim;
+        a.value_dim = value_dim; a.least = least;
+        // as many value columns per CTA as the head has (the scores are made once per CTA), fewer while the launch would
+        // leave SMs without a CTA
         int cb = columns_per_cta;
         if (cb <= 0) {
             cb = 64;
-            while (cb > 16 && ((long long)n_long * heads * ((value_dim + cb - 1) / cb) < 148 || cb / 2 >= value_dim)) cb /= 2;
+            while (cb > 16 && ((long long)n_chunks * heads * ((value_dim + cb - 1) / cb) < 148 || cb / 2 >= value_dim)) cb /= 2;
         }
-        while (cb > 16 && chunk_smem(key_dim, cb) > 200 * 1024) cb /= 2;
-        if (chunk_smem(key_dim, cb) > 227 * 1024) return -3;
-#define LIGHTNING_CHUNKS(CPT) launch_chunks<CPT>(proj, stride, q_col, k_col, v_col, decay, state, state_stride, req_slot, q_start, q_len, o, \
-                                                 heads, key_dim, value_dim, n_req, least, s)
-        st = cb >= 64 ? LIGHTNING_CHUNKS(4) : cb >= 32 ? LIGHTNING_CHUNKS(2) : LIGHTNING_CHUNKS(1);
-#undef LIGHTNING_CHUNKS
+        while (cb > 16 && reads_smem(key_dim, cb) > 110 * 1024 && reads_smem(key_dim, cb / 2) <= 110 * 1024) cb /= 2;   // two CTAs per SM
+        if (reads_smem(key_dim, cb) > 227 * 1024) return -3;
+        st = cb >= 64 ? launch_chunks<4>(a, n_req, n_chunks, s) : cb >= 32 ? launch_chunks<2>(a, n_req, n_chunks, s) : launch_chunks<1>(a, n_req, n_chunks, s);
         if (st) return st;
     }
     if (least <= 0 || n_short > 0) {

@@ -959,13 +959,14 @@ def lightning_jobs():
 
 def lightning_recurrence(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor,
                          req_slot: torch.Tensor, q_start: torch.Tensor, q_len: torch.Tensor, n_req: int, o: torch.Tensor, heads: int,
-                         key_dim: int, value_dim: int, least: int = 0, n_long: int = 0, n_short: int = 0, columns_per_cta: int = 0) -> torch.Tensor:
+                         key_dim: int, value_dim: int, least: int = 0, n_short: int = 0, chunks=None, columns_per_cta: int = 0) -> torch.Tensor:
     """Per head S <- decay S + silu(k) silu(v)^T, o = S^T silu(q) over each request's tokens in order.  proj float
     [tokens, columns] holds the projections' sums (q and k: heads x key_dim from `q_col` / `k_col`; v: heads x value_dim
     from `v_col`); state float [slots, heads * value_dim * key_dim] is read and advanced; o float [tokens, heads *
-    value_dim].  `least` > 0: the `n_long` requests that bring at least that many tokens run chunk by chunk, the
-    `n_short` others token by token (the host knows the counts from the step's shape); 0: all token by token.
-    `columns_per_cta` (16, 32, 64; 0: by the size of the launch): value columns a CTA of the chunked form takes."""
+    value_dim].  `least` > 0 with `chunks` = (chunk_req, chunk_t0, req_chunk0, n_chunks): the requests that bring at least
+    that many tokens run chunk by chunk (per chunk of LIGHTNING_CHUNK tokens its request and its first token inside the
+    portion, per request the index of its first chunk: int32 on the device), the `n_short` others token by token; 0: all
+    token by token.  `columns_per_cta` (16, 32, 64; 0: by the size of the launch): value columns a CTA of the chunked form takes."""
     _need(proj, torch.float32, "proj", 2); _need(decay, torch.float32, "decay", 1); _need(state, torch.float32, "state", 2)
     _need(o, torch.float32, "o", 2)
     for name, t in (("req_slot", req_slot), ("q_start", q_start), ("q_len", q_len)):
@@ -974,11 +975,21 @@ def lightning_recurrence(proj: torch.Tensor, q_col: int, k_col: int, v_col: int,
     if (decay.numel() != heads or state.shape[1] != heads * key_dim * value_dim or o.shape != (tokens, heads * value_dim)
             or max(q_col, k_col) + heads * key_dim > cols or v_col + heads * value_dim > cols or key_dim > LIGHTNING_MAX_KEY_DIM):
         raise KernelError("lightning_recurrence: shapes disagree")
-    both = least > 0 and n_long > 0 and n_short > 0
+    chunk_req = chunk_t0 = req_chunk0 = scratch = None
+    n_chunks = 0
+    if least > 0 and chunks is not None and chunks[3] > 0:
+        chunk_req, chunk_t0, req_chunk0, n_chunks = chunks
+        for name, t in (("chunk_req", chunk_req), ("chunk_t0", chunk_t0), ("req_chunk0", req_chunk0)):
+            _need(t, torch.int32, name, 1)
+        if chunk_req.numel() < n_chunks or chunk_t0.numel() < n_chunks or req_chunk0.numel() < n_req:
+            raise KernelError("lightning_recurrence: the chunk lists are too short")
+        scratch = torch.empty((n_chunks, heads, key_dim, value_dim), dtype=torch.float32, device=proj.device)
+    launches = (3 if n_chunks else 0) + (1 if not n_chunks or n_short else 0)
     _check(_lightning().cisr_lightning_recurrence(_p(proj), cols, q_col, k_col, v_col, _p(decay), _p(state), ctypes.c_longlong(state.shape[1]),
-                                                  _p(req_slot), _p(q_start), _p(q_len), _p(o), heads, key_dim, value_dim, n_req, int(least),
-                                                  int(n_long), int(n_short), int(columns_per_cta), _stream()), "lightning_recurrence",
-           own=2 if both else 1)
+                                                  _p(req_slot), _p(q_start), _p(q_len), _p(o), heads, key_dim, value_dim, n_req,
+                                                  int(least if n_chunks else 0), int(n_chunks), int(n_short), _p(chunk_req), _p(chunk_t0),
+                                                  _p(req_chunk0), _p(scratch), int(columns_per_cta), _stream()), "lightning_recurrence",
+           own=launches)
     return o
 
 
@@ -1795,7 +1806,7 @@ _DESCRIBE = {
     "diff_rope_rows": lambda proj, k_col, v_col, **kw: (int(proj.shape[0]), int(proj.shape[1]), int(kw["q_out"].shape[1] * kw["q_out"].shape[2]),
                                                         0 if kw.get("k_cache") is None else int(kw["k_cache"].shape[1] * kw["k_cache"].shape[3])),
     "lightning_recurrence": lambda proj, q_col, k_col, v_col, decay, state, req_slot, q_start, q_len, n_req, o, heads, key_dim, value_dim, **kw:
-        (int(proj.shape[0]), int(n_req), int(heads), int(key_dim), int(value_dim), int(kw.get("n_long", 0))),
+        (int(proj.shape[0]), int(n_req), int(heads), int(key_dim), int(value_dim), int(kw["chunks"][3]) if kw.get("chunks") else 0),
     "lightning_output": lambda o, *a, **kw: (int(o.shape[0]), int(o.shape[1])),
     "diff_combine": lambda mixed, gate, gate_col, out, *a: (int(out.shape[0]), int(out.shape[1]), int(mixed.shape[1] * mixed.shape[2])),
     "depth_mix_norm": lambda hist, x, pending, w, n_new, **kw:

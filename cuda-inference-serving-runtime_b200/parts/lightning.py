@@ -27,10 +27,20 @@ LIGHTNING_PLAN_KEY = ("lightning_chunks", CHUNKED_FROM)
 DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "norm": "norm", "o": "o"}
 
 
-def long_and_short(q_len) -> tuple:
-    """How many of a step's requests bring at least CHUNKED_FROM tokens, and how many fewer."""
-    n_long = sum(1 for n in q_len if n >= CHUNKED_FROM)
-    return n_long, len(q_len) - n_long
+def chunk_plan(q_len) -> tuple:
+    """Which chunks the chunked recurrence runs for a step whose requests bring `q_len` tokens: per chunk its request and
+    its first token inside the portion, per request the index of its first chunk; and how many requests stay with the
+    token-by-token kernel.  Depends on the portion lengths alone, so steps of one shape share it."""
+    chunk_req, chunk_t0, req_chunk0, short = [], [], [], 0
+    for r, n in enumerate(q_len):
+        req_chunk0.append(len(chunk_req))
+        if n < CHUNKED_FROM:
+            short += 1
+            continue
+        for t0 in range(0, n, kernels.LIGHTNING_CHUNK):
+            chunk_req.append(r)
+            chunk_t0.append(t0)
+    return chunk_req, chunk_t0, req_chunk0, short
 
 
 @register(MIXERS, "lightning")
@@ -87,19 +97,23 @@ class LightningAttention(Mixer):
         return LIGHTNING_PLAN_KEY
 
     def step_plan(self, host):
+        import numpy as np
+
         from ..engine.batch import StepPlan
-        n_long, n_short = long_and_short(host.q_len)
-        return StepPlan(arrays={}, info={"n_long": n_long, "n_short": n_short})
+        chunk_req, chunk_t0, req_chunk0, short = chunk_plan(host.q_len)
+        as_i32 = lambda values: np.asarray(values, dtype=np.int32)
+        return StepPlan(arrays={"chunk_req": as_i32(chunk_req), "chunk_t0": as_i32(chunk_t0), "req_chunk0": as_i32(req_chunk0)},
+                        info={"n_chunks": len(chunk_req), "n_short": short})
 
     def forward(self, h, ctx, cache):
         tokens = ctx.n_tokens
         proj = linear(as_tensor(h), self.w_in)                      # float [tokens, q | k | v | gate | padding]
         o = torch.empty((tokens, self.nv), dtype=torch.float32, device=ctx.device)
         plan = ctx.plan_for(self)
+        chunks = (plan["chunk_req"], plan["chunk_t0"], plan["req_chunk0"], plan.info["n_chunks"]) if plan.info["n_chunks"] else None
         kernels.lightning_recurrence(proj, 0, self.nqk, 2 * self.nqk, self.decay, cache.state, ctx.req_slot, ctx.q_start, ctx.q_len,
                                      ctx.n_requests, o, self.heads, self.key_dim, self.value_dim,
-                                     least=CHUNKED_FROM if plan.info["n_long"] else 0, n_long=plan.info["n_long"],
-                                     n_short=plan.info["n_short"])
+                                     least=CHUNKED_FROM if chunks else 0, n_short=plan.info["n_short"], chunks=chunks)
         width = self.o.shape[1]
         make = torch.zeros if width != self.nv else torch.empty
         gated = make((tokens, width), dtype=self.dtype, device=ctx.device)

@@ -96,9 +96,12 @@ def test_cache_groups_states_and_shared_rows():
     assert all(g.pool.n_free == g.pool.n_pages for g in cache.page_groups)
 
 
-def test_the_recurrences_launch_plan_counts_long_and_short_portions():
-    from cisr_b200.parts.lightning import CHUNKED_FROM, long_and_short
-    assert long_and_short([1, CHUNKED_FROM - 1, CHUNKED_FROM, 500, 2]) == (2, 3) and long_and_short([1, 1]) == (0, 2)
+def test_the_recurrences_launch_plan_lists_the_chunks_of_long_portions():
+    from cisr_b200.parts.lightning import CHUNKED_FROM, chunk_plan
+    C = CHUNKED_FROM
+    chunk_req, chunk_t0, req_chunk0, short = chunk_plan([1, C - 1, C, 2 * C + 5, 2])
+    assert (chunk_req, chunk_t0, req_chunk0, short) == ([2, 3, 3, 3], [0, 0, C, 2 * C], [0, 0, 0, 1, 4], 3)
+    assert chunk_plan([1, 1]) == ([], [], [0, 0], 2)
 
 
 @pytest.mark.parametrize("base, dims, scaling", [(10000.0, 24, (8.0, 1.0, 4.0, 1024)), (500.0, 16, (8.0, 1.0, 2.0, 40)), (10000.0, 64, (3.0, 2.0, 16.0, 300))])

@@ -115,11 +115,19 @@ def test_recurrence_token_by_token_and_chunk_by_chunk(heads, dk, dv, columns):
         sizes = [cuts[r].pop(0) for r in batch]
         proj = torch.cat([us[r][at[r]:at[r] + n] for r, n in zip(batch, sizes)]).cuda().contiguous()
         q_start = np.cumsum([0] + sizes[:-1]).astype(np.int32)
-        n_long = sum(n >= kernels.LIGHTNING_CHUNK for n in sizes)
+        chunk_req, chunk_t0, req_chunk0 = [], [], []          # the chunks of the portions that are long enough, request by request
+        for i, n in enumerate(sizes):
+            req_chunk0.append(len(chunk_req))
+            if n >= kernels.LIGHTNING_CHUNK:
+                for t0 in range(0, n, kernels.LIGHTNING_CHUNK):
+                    chunk_req.append(i)
+                    chunk_t0.append(t0)
+        n_short = sum(n < kernels.LIGHTNING_CHUNK for n in sizes)
         o = torch.full((proj.shape[0], nv), 7.0, device="cuda")
         kernels.lightning_recurrence(proj, 0, nqk, 2 * nqk, decay.cuda(), state, dev([slot[r] for r in batch]), dev(q_start), dev(sizes),
-                                     len(batch), o, heads, dk, dv, least=kernels.LIGHTNING_CHUNK if n_long else 0, n_long=n_long,
-                                     n_short=len(sizes) - n_long, columns_per_cta=columns)
+                                     len(batch), o, heads, dk, dv, least=kernels.LIGHTNING_CHUNK if chunk_req else 0, n_short=n_short,
+                                     chunks=(dev(chunk_req), dev(chunk_t0), dev(req_chunk0), len(chunk_req)) if chunk_req else None,
+                                     columns_per_cta=columns)
         for i, (r, n) in enumerate(zip(batch, sizes)):
             got[r].append(o[q_start[i]:q_start[i] + n].double().cpu())
             at[r] += n
