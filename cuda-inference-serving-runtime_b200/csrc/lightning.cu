@@ -111,19 +111,39 @@ struct ChunkArgs {
 };
 
 // silu of one projection of the chunk's tokens, coordinate-major into dst [dP][LD]; zero beyond the portion and the width
+// (a thread asks for eight of its numbers before it uses the first: eight loads in flight instead of one)
 __device__ __forceinline__ void stage_transposed(const ChunkArgs& a, int col0, int token0, int n, int dP, float* dst) {
-    for (int i = threadIdx.x; i < C * dP; i += 256) {
-        const int t = i / dP, kk = i - t * dP;
-        dst[kk * LD + t] = (t < n && kk < a.key_dim) ? silu_f(a.proj[(size_t)(token0 + t) * a.stride + col0 + kk]) : 0.f;
+    const float* __restrict__ src = a.proj + (size_t)token0 * a.stride + col0;
+    for (int i0 = threadIdx.x; i0 < C * dP; i0 += 8 * 256) {
+        float raw[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * 256, t = i / dP, kk = i - t * dP;
+            raw[u] = (i < C * dP && t < n && kk < a.key_dim) ? src[(size_t)t * a.stride + kk] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * 256, t = i / dP, kk = i - t * dP;
+            if (i < C * dP) dst[kk * LD + t] = silu_f(raw[u]);       // silu(0) = 0: beyond the portion and the width
+        }
     }
 }
 // silu(v) of the CTA's columns into V [C][CB], each row times weight(t) (zero beyond the portion and the width)
 template <int CB, typename W>
 __device__ __forceinline__ void stage_values(const ChunkArgs& a, int h, int c0, int token0, int n, float* V, W weight) {
-    for (int i = threadIdx.x; i < C * CB; i += 256) {
-        const int t = i / CB, c = i - t * CB;
-        V[i] = (t < n && c0 + c < a.value_dim)
-                   ? silu_f(a.proj[(size_t)(token0 + t) * a.stride + a.v_col + h * a.value_dim + c0 + c]) * weight(t) : 0.f;
+    const float* __restrict__ src = a.proj + (size_t)token0 * a.stride + a.v_col + h * a.value_dim + c0;
+    for (int i0 = threadIdx.x; i0 < C * CB; i0 += 4 * 256) {      // C * CB is a multiple of 1024
+        float raw[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * 256, t = i / CB, c = i - t * CB;
+            raw[u] = (t < n && c0 + c < a.value_dim) ? src[(size_t)t * a.stride + c] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * 256, t = i / CB;
+            V[i] = t < n ? silu_f(raw[u]) * weight(t) : 0.f;
+        }
     }
 }
 __device__ __forceinline__ void stage_powers(float decay, float* pw) {
@@ -201,13 +221,20 @@ __global__ void __launch_bounds__(256) lightning_scan_kernel(ChunkArgs a) {
     const size_t step = (size_t)a.heads * a.key_dim * a.value_dim;
     float* block = a.scratch + ((size_t)a.req_chunk0[r] * a.heads + h) * a.key_dim * a.value_dim + e;
     const int chunks = (n_all + C - 1) / C;
-    float gain = block[0];
-    for (int c = 0; c < chunks; ++c) {
-        const float next = c + 1 < chunks ? block[(size_t)(c + 1) * step] : 0.f;      // on its way during this chunk's step
-        const int n = min(C, n_all - c * C);
-        block[(size_t)c * step] = S;
-        S = (n == C ? whole : expf((float)n * lg)) * S + gain;
-        gain = next;
+    constexpr int AHEAD = 8;                              // gains requested together: the walk itself is one multiply-add per chunk
+    for (int c0 = 0; c0 < chunks; c0 += AHEAD) {
+        float gain[AHEAD];
+#pragma unroll
+        for (int u = 0; u < AHEAD; ++u) gain[u] = c0 + u < chunks ? block[(size_t)(c0 + u) * step] : 0.f;
+#pragma unroll
+        for (int u = 0; u < AHEAD; ++u) {
+            const int c = c0 + u;
+            if (c < chunks) {
+                const int n = min(C, n_all - c * C);
+                block[(size_t)c * step] = S;
+                S = (n == C ? whole : expf((float)n * lg)) * S + gain[u];
+            }
+        }
     }
     *kept = S;
 }
@@ -258,9 +285,16 @@ __global__ void __launch_bounds__(256) lightning_reads_kernel(ChunkArgs a) {
     }
     __syncthreads();                                      // the scores are made: the keys' place takes the state's columns
     const float* block = a.scratch + ((size_t)chunk * a.heads + h) * a.key_dim * a.value_dim;
-    for (int i = tid; i < dP * CB; i += 256) {
-        const int row = i / CB, c = i - row * CB;
-        S[i] = (row < a.key_dim && c0 + c < a.value_dim) ? block[(size_t)row * a.value_dim + c0 + c] : 0.f;
+    for (int i0 = tid; i0 < dP * CB; i0 += 8 * 256) {
+        float raw[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * 256, row = i / CB, c = i - row * CB;
+            raw[u] = (i < dP * CB && row < a.key_dim && c0 + c < a.value_dim) ? block[(size_t)row * a.value_dim + c0 + c] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (i0 + u * 256 < dP * CB) S[i0 + u * 256] = raw[u];
     }
     __syncthreads();
     float acc[4][CPT] = {}, carried[4][CPT] = {};
