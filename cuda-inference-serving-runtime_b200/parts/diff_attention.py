@@ -29,7 +29,7 @@ from ..config.spec import CacheUse
 from ..ops import kernels
 from .attention import ATTENTION_PLAN_KEY, attention_step_plan, paged_attention
 from .base import MIXERS, POSITIONS, Mixer, TensorNeed, build_part, register
-from .linear import as_tensor, linear, linear_to_stream
+from .linear import linear_normed, linear_to_stream
 
 DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "o": "o", "q_conv": "q.conv", "k_conv": "k.conv", "v_conv": "v.conv",
                  "lq1": "lq1", "lk1": "lk1", "lq2": "lq2", "lk2": "lk2"}
@@ -141,7 +141,7 @@ class DiffAttention(Mixer):
         if self.taps and cache.state is None:
             raise ValueError("diff_attention needs its side state (the convolution's kept inputs) from the cache manager")
         tokens = ctx.n_tokens
-        proj = linear(as_tensor(h), self.w_in)                      # float [tokens, q (| k | v) (| gate)]
+        proj = linear_normed(h, self.w_in, tokens)                  # float [tokens, q (| k | v) (| gate)]
         q = torch.empty((tokens, 2 * self.hq, self.width), dtype=self.dtype, device=ctx.device)
         if not self.taps:
             rot = self.position.rotation(ctx) if self.position is not None else None

@@ -20,7 +20,7 @@ from ..config.spec import CacheUse
 from ..ops import kernels
 from .base import MIXERS, Mixer, TensorNeed, register
 from .feedforward import pad_columns
-from .linear import as_tensor, linear, linear_to_stream
+from .linear import linear_normed, linear_to_stream
 
 CHUNKED_FROM = kernels.LIGHTNING_CHUNK
 LIGHTNING_PLAN_KEY = ("lightning_chunks", CHUNKED_FROM)
@@ -107,7 +107,7 @@ class LightningAttention(Mixer):
 
     def forward(self, h, ctx, cache):
         tokens = ctx.n_tokens
-        proj = linear(as_tensor(h), self.w_in)                      # float [tokens, q | k | v | gate | padding]
+        proj = linear_normed(h, self.w_in, tokens)                  # float [tokens, q | k | v | gate | padding]
         o = torch.empty((tokens, self.nv), dtype=torch.float32, device=ctx.device)
         plan = ctx.plan_for(self)
         chunks = (plan["chunk_req"], plan["chunk_t0"], plan["req_chunk0"], plan.info["n_chunks"]) if plan.info["n_chunks"] else None

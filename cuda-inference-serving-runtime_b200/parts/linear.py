@@ -48,6 +48,19 @@ def norm_fusable(h, tokens: int, w: torch.Tensor) -> bool:
     return not (kernels.stream_takes(tokens, w) and tokens > 2)
 
 
+def linear_normed(h, w: torch.Tensor, tokens: int) -> torch.Tensor:
+    """The first product of a sub-block, float [tokens, out]: where `h` is a pending norm that the weight-streaming
+    kernel can take as its prologue (few tokens), the residual add, the norm and the product are one launch; otherwise
+    the norm's own kernel runs first."""
+    if norm_fusable(h, tokens, w):
+        out = torch.empty((tokens, w.shape[0]), dtype=torch.float32, device=w.device)
+        x_out = h.new_stream_buffer()
+        kernels.skinny_gemm(w, tokens, x=h.x, delta=h.delta, norm_w=h.weight, eps=h.eps, x_out=x_out, epilogue=kernels.EPI_PLAIN, out=out)
+        h.done(x_out)
+        return out
+    return linear(as_tensor(h), w)
+
+
 def as_tensor(h) -> torch.Tensor:
     from .base import PendingNorm
     return h.materialize_once() if isinstance(h, PendingNorm) else h
