@@ -207,36 +207,51 @@ __global__ void __launch_bounds__(256) lightning_gains_kernel(ChunkArgs a) {
     }
 }
 
-// grid (requests, heads, elements / 256): thread e owns element (row, col) = (e / value_dim, e % value_dim) of the head's state
+// grid (requests, heads, elements / (256 VEC)): a thread owns VEC neighbouring elements (row, col .. col + VEC - 1) of the
+// head's state (VEC 4 where value_dim is a multiple of 4, so that a CTA reads 4 KB in one piece from every block; else 1)
+template <int VEC>
 __global__ void __launch_bounds__(256) lightning_scan_kernel(ChunkArgs a) {
     pdl_trigger();
     pdl_wait();
-    const int r = blockIdx.x, h = blockIdx.y, e = blockIdx.z * 256 + threadIdx.x;
+    const int r = blockIdx.x, h = blockIdx.y, e = (blockIdx.z * 256 + threadIdx.x) * VEC;
     const int n_all = a.q_len[r];
     if (n_all < a.least || e >= a.key_dim * a.value_dim) return;
     const int row = e / a.value_dim, col = e - row * a.value_dim;
     float* kept = a.state + (size_t)a.req_slot[r] * a.state_stride + ((size_t)h * a.value_dim + col) * a.key_dim + row;
-    float S = *kept;
+    float S[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) S[j] = kept[(size_t)j * a.key_dim];
     const float lg = logf(a.decay[h]), whole = expf((float)C * lg);
     const size_t step = (size_t)a.heads * a.key_dim * a.value_dim;
     float* block = a.scratch + ((size_t)a.req_chunk0[r] * a.heads + h) * a.key_dim * a.value_dim + e;
     const int chunks = (n_all + C - 1) / C;
-    constexpr int AHEAD = 8;                              // gains requested together: the walk itself is one multiply-add per chunk
+    constexpr int AHEAD = VEC == 1 ? 8 : 4;               // gains requested together: the walk itself is one multiply-add per chunk
     for (int c0 = 0; c0 < chunks; c0 += AHEAD) {
-        float gain[AHEAD];
+        float gain[AHEAD][VEC];
 #pragma unroll
-        for (int u = 0; u < AHEAD; ++u) gain[u] = c0 + u < chunks ? block[(size_t)(c0 + u) * step] : 0.f;
+        for (int u = 0; u < AHEAD; ++u) {
+            if (VEC == 4) {
+                const float4 g = c0 + u < chunks ? *reinterpret_cast<const float4*>(block + (size_t)(c0 + u) * step) : make_float4(0.f, 0.f, 0.f, 0.f);
+                gain[u][0] = g.x; gain[u][1 % VEC] = g.y; gain[u][2 % VEC] = g.z; gain[u][3 % VEC] = g.w;
+            } else {
+                gain[u][0] = c0 + u < chunks ? block[(size_t)(c0 + u) * step] : 0.f;
+            }
+        }
 #pragma unroll
         for (int u = 0; u < AHEAD; ++u) {
             const int c = c0 + u;
             if (c < chunks) {
                 const int n = min(C, n_all - c * C);
-                block[(size_t)c * step] = S;
-                S = (n == C ? whole : expf((float)n * lg)) * S + gain[u];
+                const float f = n == C ? whole : expf((float)n * lg);
+                if (VEC == 4) *reinterpret_cast<float4*>(block + (size_t)c * step) = make_float4(S[0], S[1 % VEC], S[2 % VEC], S[3 % VEC]);
+                else block[(size_t)c * step] = S[0];
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) S[j] = f * S[j] + gain[u][j];
             }
         }
     }
-    *kept = S;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) kept[(size_t)j * a.key_dim] = S[j];
 }
 
 template <int CPT>
@@ -259,28 +274,39 @@ __global__ void __launch_bounds__(256) lightning_reads_kernel(ChunkArgs a) {
     stage_transposed(a, a.k_col + h * a.key_dim, token0, n, dP, Kt);
     stage_values<CB>(a, h, c0, token0, n, V, [](int) { return 1.f; });
     __syncthreads();
-    // scores of the chunk: P[t][i] = decay^(t - i) (q_t . k_i) for i <= t
+    // scores of the chunk: P[t][i] = decay^(t - i) (q_t . k_i) for i <= t.  The 136 tiles of 4 x 4 on and below the diagonal go
+    // to the first 136 threads (tile k = py (py + 1) / 2 + px), so five warps work and three wait instead of all eight walking
+    // the keys for a few lanes each; the tiles above the diagonal are zeroed by the other threads.
     {
-        float acc[4][4] = {};
-        if (tx <= ty) {                                // tiles above the diagonal hold nothing
+        constexpr int TILES = (C / 4) * (C / 4 + 1) / 2;
+        if (tid < TILES) {
+            int py = (int)((sqrtf(8.f * (float)tid + 1.f) - 1.f) * 0.5f);
+            while (py * (py + 1) / 2 > tid) --py;
+            while ((py + 1) * (py + 2) / 2 <= tid) ++py;
+            const int px = tid - py * (py + 1) / 2;
+            float acc[4][4] = {};
             for (int kk = 0; kk < dP; ++kk) {
-                const float4 q = *reinterpret_cast<const float4*>(Qt + kk * LD + 4 * ty);
-                const float4 k = *reinterpret_cast<const float4*>(Kt + kk * LD + 4 * tx);
+                const float4 q = *reinterpret_cast<const float4*>(Qt + kk * LD + 4 * py);
+                const float4 k = *reinterpret_cast<const float4*>(Kt + kk * LD + 4 * px);
                 const float qv[4] = {q.x, q.y, q.z, q.w}, kv[4] = {k.x, k.y, k.z, k.w};
 #pragma unroll
                 for (int x = 0; x < 4; ++x)
 #pragma unroll
                     for (int y = 0; y < 4; ++y) acc[x][y] += qv[x] * kv[y];
             }
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const int t = 4 * py + x;
+                float4 out;
+                float* ov = reinterpret_cast<float*>(&out);
+#pragma unroll
+                for (int y = 0; y < 4; ++y) { const int i = 4 * px + y; ov[y] = i <= t ? acc[x][y] * pw[t - i] : 0.f; }
+                *reinterpret_cast<float4*>(P + t * LD + 4 * px) = out;
+            }
         }
+        if (tx > ty) {
 #pragma unroll
-        for (int x = 0; x < 4; ++x) {
-            const int t = 4 * ty + x;
-            float4 out;
-            float* ov = reinterpret_cast<float*>(&out);
-#pragma unroll
-            for (int y = 0; y < 4; ++y) { const int i = 4 * tx + y; ov[y] = i <= t ? acc[x][y] * pw[t - i] : 0.f; }
-            *reinterpret_cast<float4*>(P + t * LD + 4 * tx) = out;
+            for (int x = 0; x < 4; ++x) *reinterpret_cast<float4*>(P + (4 * ty + x) * LD + 4 * tx) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
     __syncthreads();                                      // the scores are made: the keys' place takes the state's columns
@@ -360,7 +386,11 @@ static int launch_chunks(const ChunkArgs& a, int n_req, int n_chunks, cudaStream
     }
     int st = launch_kernel(lightning_gains_kernel<CPT>, dim3(n_chunks, a.heads, slabs), dim3(256), smem_g, s, g_pdl, a);
     if (st) return st;
-    st = launch_kernel(lightning_scan_kernel, dim3(n_req, a.heads, (a.key_dim * a.value_dim + 255) / 256), dim3(256), 0, s, g_pdl, a);
+    const int elements = a.key_dim * a.value_dim;
+    if (a.value_dim % 4 == 0 && ((uintptr_t)a.scratch & 15) == 0)
+        st = launch_kernel(lightning_scan_kernel<4>, dim3(n_req, a.heads, (elements / 4 + 255) / 256), dim3(256), 0, s, g_pdl, a);
+    else
+        st = launch_kernel(lightning_scan_kernel<1>, dim3(n_req, a.heads, (elements + 255) / 256), dim3(256), 0, s, g_pdl, a);
     if (st) return st;
     return launch_kernel(lightning_reads_kernel<CPT>, dim3(n_chunks, a.heads, slabs), dim3(256), smem_r, s, g_pdl, a);
 }
