@@ -94,7 +94,9 @@ class PreNormScaledBlock:
     """x += s1 * mixer(norm1(x)); x += s2 * feed_forward(norm2(x)), with s1, s2 one factor per channel; the feed-forward
     half may be absent.  The scaled add of each output is made by the norm kernel that follows it; a feed-forward that
     says `applies_output_scale` multiplies by s2 in its own last kernel instead, and its output is then pending like any
-    other (so the next layer's first product may take the add and the norm into its prologue)."""
+    other (so the next layer's first product may take the add and the norm into its prologue).  Where a scale is one
+    constant for all channels (`ChannelScale` with a `value`), the sub-block is told the constant and may add its
+    output, multiplied, to the stream in the epilogue of its last product (`parts/linear.py: linear_to_stream`)."""
 
     def __init__(self, spec: LayerSpec, dtype: torch.dtype):
         self.spec = spec

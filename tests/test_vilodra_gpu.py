@@ -286,6 +286,33 @@ def test_norm_whose_weight_is_an_offset_from_one():
         assert torch.allclose(out.double().cpu(), want, rtol=tol, atol=tol) and torch.allclose(xs.cpu(), x + delta)
 
 
+@pytest.mark.parametrize("tokens, n, k", [(3, 72, 128), (16, 320, 192), (8, 4096, 1024), (200, 136, 256), (513, 72, 64)])
+def test_products_add_into_the_stream_times_a_constant(tokens, n, k):
+    """The in-place add of a sub-block's last product with the branch multiplier as its factor, on each product kernel
+    that has it: the weight-streaming kernels for few tokens (small matrices, and the persistent one from 8 MB on) and
+    the tcgen05 product for many.  out += 0.7 * (a w^T) against float64."""
+    from cisr_b200.ops import kernels
+    g = torch.Generator().manual_seed(tokens + n)
+    a = torch.randn(tokens, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    x = torch.randn(tokens, n, generator=g)
+    want = x.to(F) + 0.7 * (a.to(F) @ w.to(F).T)
+    out = x.clone().cuda()
+    if tokens <= 16:
+        assert kernels.skinny_ok(tokens, w.cuda())
+        kernels.skinny_gemm(w.cuda(), tokens, act=a.cuda(), epilogue=kernels.EPI_PLAIN, out=out, accumulate=True, out_mult=0.7)
+    else:
+        assert kernels.tcgen05_ok(a.cuda(), w.cuda())
+        kernels.gemm_tcgen05(a.cuda(), w.cuda(), out, accumulate=True, out_mult=0.7)
+    assert torch.allclose(out.double().cpu(), want, rtol=1e-4, atol=1e-4)
+    plain = torch.empty(tokens, n, device="cuda")            # written, not added: the factor applies there too
+    if tokens <= 16:
+        kernels.skinny_gemm(w.cuda(), tokens, act=a.cuda(), epilogue=kernels.EPI_PLAIN, out=plain, out_mult=0.7)
+    else:
+        kernels.gemm_tcgen05(a.cuda(), w.cuda(), plain, out_mult=0.7)
+    assert torch.allclose(plain.double().cpu(), want - x.to(F), rtol=1e-4, atol=1e-4)
+
+
 # ------------------------------------------------------------------ one layer is the whole model
 def one_latent(window, heads=3, dim=24, rot=8, vdim=20, rank=40, scale=0.3, width=64, scaling=vm.YARN_A, mlp=None):
     return vm.one_layer(vm.latent(heads, dim, rot, vdim, rank, scale, window=window, scaling=scaling), mlp, width=width)
