@@ -512,9 +512,11 @@ def vilodra_pair(width: int, layers: int, heads: int, ff_active: int, experts: i
             return {"type": "attention", "mixer": diff, "mlp": dense}
         return {"type": "latent_attention", "mixer": lat if kind == 1 else dict(lat, kv_from=i - 2), "mlp": moe}
 
+    zur, llama = design_pair(width, layers, heads, ff_active, experts, top, vocab)
     vilo = {"architecture": "Vilodra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.7, "max_positions": 8192,
             "layers": [layer(i) for i in range(layers)]}
-    return vilo, design_pair(width, layers, heads, ff_active, experts, top, vocab)[1]
+    # beside it the Llama shape, as for every design, and Zurolorn, the design it shares the most with (latent attention, routed experts)
+    return {"vilodra": vilo, "llama": llama, "zurolorn": zur}
 
 
 DESIGN_SIZES = {"1024": (1024, 8, 16, 2048, 16, 4), "2048": (2048, 8, 32, 4096, 32, 4), "4096": (4096, 4, 32, 8192, 64, 8)}
@@ -706,7 +708,8 @@ def design_comparison(args, hbm_gbs: float, burst_tflops: float, peak_source: st
             raise SystemExit(f"--designs takes sizes from {', '.join(DESIGN_SIZES)}")
         width, layers, heads, ff_active, experts, top = DESIGN_SIZES[size]
         entry = {"width": width, "layers": layers, "heads": heads, "feed_forward_active": ff_active, "experts": experts, "top": top}
-        for name, raw in zip((args.design, "llama"), pair(width, layers, heads, ff_active, experts, top)):
+        models = pair(width, layers, heads, ff_active, experts, top)
+        for name, raw in (models.items() if isinstance(models, dict) else zip((args.design, "llama"), models)):
             model = Model.from_config(raw, seed=args.seed, dtype="bfloat16")
             prefill_ms = prefill_run(model, prompt, args.seed)
             d = device_decode(model, batch, context, min(args.steps, 64), args.warmup, args.seed, min_seconds=0.2)
